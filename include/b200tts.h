@@ -406,6 +406,65 @@ B2TTS_API int    b2tts_decoder_stack_decode(const void* x, int64_t x_row_stride,
                                             const int32_t* context_lens, int page_size, float scale,
                                             void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- token-id decoder models with a 32-bit residual stream -------------------------------------
+ * (no counterpart in the reference, whose models take embeddings and keep a bf16 residual)
+ * `dtype` selects the activation / cache / table type of the void* tensors: bf16 for serving, float for the
+ * all-32-bit mode.  The residual stream x, every norm, the router, the per-head constants and the convolution
+ * weights are float in both.  Rows whose slot is -1 and sequences whose length is 0 are CUDA-graph padding. */
+#define B2TTS_DTYPE_BF16 0
+#define B2TTS_DTYPE_F32  1
+
+/* x[r] = embed[tokens[r]] + pos_table[positions[r]] (float sum); h[r] = T(x[r] / sqrt(mean(x[r]^2) + eps) * gain[0])
+ * when h != NULL ("gain norm": one gain for all coordinates). */
+B2TTS_API int b2tts_embed_pos_norm(const int32_t* tokens, const int32_t* positions, const void* embed, const void* pos_table,
+                                   float* x, void* h, const float* gain, int rows, int cols, int vocab, int max_pos,
+                                   float eps, int dtype, void* stream);
+/* The residual update of a layer whose sublayers all read one norm, fused with the next norm:
+ * x[r] += mult * (a[r] + b[r] + sum_k zw[r, k] * z[r * top + k]) (each term optional, k in ascending order);
+ * h[r] = gain norm of the new x[r] when h != NULL. */
+B2TTS_API int b2tts_residual_norm(float* x, const void* a, const void* b, const void* z, const float* zw, int top, float mult,
+                                  void* h, const float* gain, int rows, int cols, float eps, int dtype, void* stream);
+/* out[i] = gain norm of x[rows_idx[i]] (rows_idx NULL = row i). */
+B2TTS_API int b2tts_gather_gain_norm(const float* x, const int32_t* rows_idx, void* out, const float* gain, int rows, int cols,
+                                     float eps, int dtype, void* stream);
+/* y <- max(y, 0)^2 in place. */
+B2TTS_API int b2tts_relu_sq(void* y, int64_t n, int dtype, void* stream);
+/* Short causal convolution over time on every channel of the merged projection u [n, C] = [q | k | v]
+ * (C = heads*dim + kv_heads*dim + kv_heads*vdim; conv_w [C, taps] float, tap taps-1 is the token itself), then RMS norm
+ * per head over dim with q_norm_w / k_norm_w [dim] for q and k; q goes to q_out [n, heads*dim], k and v to their cache
+ * slot (slot_mapping[n]).  Token n belongs to batch row tok_seq[n] at position positions[n]; row b brings seq_len[b]
+ * tokens starting at batch index seq_start[b] and position seq_pos0[b], and owns state slot seq_slot[b]:
+ * state [slots, taps-1, C] holds the last taps-1 projections of the sequence (oldest first) and is advanced by this
+ * call.  Positions before 0 read as zero whatever the slot holds, so a slot needs no clearing between owners. */
+B2TTS_API int b2tts_conv_headnorm_kvwrite(const void* u, int64_t u_stride, const float* conv_w, void* state,
+                                          const int32_t* tok_seq, const int32_t* positions, const int32_t* seq_start,
+                                          const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* seq_slot,
+                                          const int32_t* slot_mapping, const float* q_norm_w, const float* k_norm_w,
+                                          void* q_out, void* k_cache, void* v_cache, int n_tokens, int n_seqs, int heads,
+                                          int kv_heads, int dim, int vdim, int taps, float eps, int dtype, void* stream);
+/* Sliding-window attention with un-normalised sigmoid weights and a logarithmic distance bias over the paged cache:
+ * out[i, h] = sum_{0 <= i-j < window} sigmoid(q_ih . k_jg * scale - r1[h] * ln(1 + r2[h] * (i-j)) + pb[h]) * v_jg.
+ * q [n, heads*dim], caches [slots, kv_heads*dim] / [slots, kv_heads*vdim], out [n, heads*vdim]; key j of batch row b lives
+ * in slot block_tables[b, j / page] * page + j % page (this step's keys included: write them first).  max_new >= every
+ * seq_len[b] sizes the grid. */
+B2TTS_API int b2tts_window_sigmoid_attn(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                        const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len,
+                                        const int32_t* block_tables, int bt_stride, const float* r1, const float* r2,
+                                        const float* pb, int n_seqs, int max_new, int heads, int kv_heads, int dim, int vdim,
+                                        int page, int window, float scale, int dtype, void* stream);
+/* Sigmoid top-k router: scores = sigmoid(h router^T) in float; top_idx [n, top] the `top` largest (ties: lower index),
+ * top_w = score / (sum of the chosen + 1e-20) * scale; then the (token, choice) pairs grouped by expert:
+ * offsets [experts + 1], sorted_pair [n * top] (pair = token * top + choice; order inside a group unspecified). */
+B2TTS_API int b2tts_moe_route(const void* h, const float* router, int32_t* top_idx, float* top_w, int32_t* offsets,
+                              int32_t* sorted_pair, int n_tokens, int cols, int experts, int top, float scale, int dtype,
+                              void* stream);
+/* C[out_row(s), :] = act(A[in_row(s), :] W[e]^T) for s in offsets[e] .. offsets[e+1], W [experts, n, k];
+ * in_row(s) = sorted_pair[s] / top if in_by_token else s; out_row(s) = sorted_pair[s] if out_by_pair else s;
+ * act 0 = none, 1 = squared ReLU; float accumulation. */
+B2TTS_API int b2tts_grouped_gemm(const void* a, int64_t lda, const void* w, void* c, int64_t ldc, const int32_t* offsets,
+                                 const int32_t* sorted_pair, int n_pairs, int experts, int n, int k, int top, int in_by_token,
+                                 int out_by_pair, int act, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -79,6 +79,14 @@ def _load():
         "b2tts_decoder_stack_plan": (I, [I, I, I, I, P, P]),
         "b2tts_decoder_stack_workspace_bytes": (Z, [I, I, I, I]),
         "b2tts_decoder_stack_decode": (I, [P, L, P, L, P, I, P, I, I, I, I, I, I, F, I, P, P, F, P, P, I, P, I, F, P, Z, P]),
+        "b2tts_embed_pos_norm": (I, [P, P, P, P, P, P, P, I, I, I, I, F, I, P]),
+        "b2tts_residual_norm": (I, [P, P, P, P, P, I, F, P, P, I, I, F, I, P]),
+        "b2tts_gather_gain_norm": (I, [P, P, P, P, I, I, F, I, P]),
+        "b2tts_relu_sq": (I, [P, L, I, P]),
+        "b2tts_conv_headnorm_kvwrite": (I, [P, L, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P]),
+        "b2tts_window_sigmoid_attn": (I, [P, P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P]),
+        "b2tts_moe_route": (I, [P, P, P, P, P, P, I, I, I, I, F, I, P]),
+        "b2tts_grouped_gemm": (I, [P, L, P, P, L, P, P, I, I, I, I, I, I, I, I, I, P]),
     }
     for name, (res, args) in sig.items():
         if not hasattr(lib, name):
@@ -669,3 +677,96 @@ def float_to_pcm16(wav: torch.Tensor, volume: float = 1.0, out: torch.Tensor | N
     _check(_load().b2tts_float_to_pcm16(wav.data_ptr(), out.data_ptr(), wav.numel(), float(volume), _stream()),
            "float_to_pcm16")
     return out
+
+
+# ------------------------------------------------------------------------------------------ token-id decoder models
+DTYPE_CODE = {torch.bfloat16: 0, torch.float32: 1}
+
+
+def _act(t: torch.Tensor, name: str) -> int:
+    """The dtype code of an activation / cache tensor (bf16 or float32, CUDA, contiguous)."""
+    _cuda(t, None, name)
+    if t.dtype not in DTYPE_CODE:
+        raise RuntimeError(f"libb200tts: `{name}` must be bfloat16 or float32, got {t.dtype}")
+    if not t.is_contiguous():
+        raise RuntimeError(f"libb200tts: `{name}` must be contiguous")
+    return DTYPE_CODE[t.dtype]
+
+
+def embed_pos_norm(tokens, positions, embed, pos_table, x, h, gain, eps):
+    """x [n, D] float <- embed[tokens] + pos_table[positions]; h [n, D] <- gain norm of x (h may be None)."""
+    dt = _act(embed, "embed")
+    _cuda(tokens, I32, "tokens"); _cuda(positions, I32, "positions"); _cuda(x, F32, "x"); _cuda(gain, F32, "gain")
+    assert pos_table.dtype == embed.dtype and (h is None or h.dtype == embed.dtype)
+    n, cols = x.shape
+    _check(_load().b2tts_embed_pos_norm(tokens.data_ptr(), positions.data_ptr(), embed.data_ptr(), pos_table.data_ptr(),
+                                        x.data_ptr(), _ptr(h), gain.data_ptr(), n, cols, embed.shape[0], pos_table.shape[0],
+                                        eps, dt, _stream()), "embed_pos_norm")
+
+
+def residual_norm(x, a, b, z, zw, mult, h, gain, eps, dtype):
+    """x += mult * (a + b + sum_k zw[:, k] * z[:, k]); h <- gain norm of the new x.  a, b, z, h optional."""
+    _cuda(x, F32, "x")
+    n, cols = x.shape
+    top = 0 if z is None else zw.shape[1]
+    for t in (a, b, z, h):
+        assert t is None or (t.dtype == dtype and t.is_contiguous())
+    _check(_load().b2tts_residual_norm(x.data_ptr(), _ptr(a), _ptr(b), _ptr(z), _ptr(zw), top, mult, _ptr(h), _ptr(gain),
+                                       n, cols, eps, DTYPE_CODE[dtype], _stream()), "residual_norm")
+
+
+def gather_gain_norm(x, rows, gain, eps, dtype, out=None):
+    _cuda(x, F32, "x")
+    n = x.shape[0] if rows is None else rows.shape[0]
+    if out is None:
+        out = torch.empty(n, x.shape[1], dtype=dtype, device=x.device)
+    _check(_load().b2tts_gather_gain_norm(x.data_ptr(), _ptr(rows), out.data_ptr(), gain.data_ptr(), n, x.shape[1], eps,
+                                          DTYPE_CODE[dtype], _stream()), "gather_gain_norm")
+    return out
+
+
+def relu_sq_(y):
+    _check(_load().b2tts_relu_sq(y.data_ptr(), y.numel(), _act(y, "y"), _stream()), "relu_sq")
+    return y
+
+
+def conv_headnorm_kvwrite(u, conv_w, state, lay, q_norm_w, k_norm_w, q_out, k_cache, v_cache, heads, kv_heads, dim, vdim,
+                          taps, eps):
+    """``lay``: the step's device layout (tok_seq, positions, seq_start, seq_pos0, seq_len, seq_slot, slot_mapping as
+    int32 tensors, n_tokens, n_seqs)."""
+    dt = _act(u, "u")
+    assert k_cache.dtype == u.dtype and v_cache.dtype == u.dtype and q_out.dtype == u.dtype
+    _check(_load().b2tts_conv_headnorm_kvwrite(
+        u.data_ptr(), u.stride(0), conv_w.data_ptr(), _ptr(state), lay.tok_seq.data_ptr(), lay.positions.data_ptr(),
+        lay.seq_start.data_ptr(), lay.seq_pos0.data_ptr(), lay.seq_len.data_ptr(), lay.seq_slot.data_ptr(),
+        lay.slot_mapping.data_ptr(), q_norm_w.data_ptr(), k_norm_w.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(),
+        v_cache.data_ptr(), lay.n_tokens, lay.n_seqs, heads, kv_heads, dim, vdim, taps, eps, dt, _stream()),
+        "conv_headnorm_kvwrite")
+
+
+def window_sigmoid_attn(q, k_cache, v_cache, out, lay, r1, r2, pb, heads, kv_heads, dim, vdim, page, window, scale):
+    dt = _act(q, "q")
+    assert k_cache.dtype == q.dtype and v_cache.dtype == q.dtype and out.dtype == q.dtype
+    _check(_load().b2tts_window_sigmoid_attn(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), lay.seq_start.data_ptr(),
+        lay.seq_pos0.data_ptr(), lay.seq_len.data_ptr(), lay.block_tables.data_ptr(), lay.block_tables.stride(0),
+        r1.data_ptr(), r2.data_ptr(), pb.data_ptr(), lay.n_seqs, lay.max_new, heads, kv_heads, dim, vdim, page, window,
+        scale, dt, _stream()), "window_sigmoid_attn")
+
+
+def moe_route(h, router, top_idx, top_w, offsets, sorted_pair, top, scale):
+    dt = _act(h, "h")
+    _cuda(router, F32, "router")
+    n, cols = h.shape
+    _check(_load().b2tts_moe_route(h.data_ptr(), router.data_ptr(), top_idx.data_ptr(), top_w.data_ptr(), offsets.data_ptr(),
+                                   sorted_pair.data_ptr(), n, cols, router.shape[0], top, scale, dt, _stream()), "moe_route")
+
+
+def grouped_gemm(a, w, c, offsets, sorted_pair, n_pairs, top, in_by_token, out_by_pair, act):
+    """w [E, N, K]; see b2tts_grouped_gemm."""
+    dt = _act(a, "a")
+    assert w.dtype == a.dtype and c.dtype == a.dtype and w.is_contiguous()
+    e, n, k = w.shape
+    _check(_load().b2tts_grouped_gemm(a.data_ptr(), a.stride(0), w.data_ptr(), c.data_ptr(), c.stride(0), offsets.data_ptr(),
+                                      sorted_pair.data_ptr(), n_pairs, e, n, k, top, int(in_by_token), int(out_by_pair), int(act),
+                                      dt, _stream()), "grouped_gemm")

@@ -98,6 +98,111 @@ def qwen3_tts_config(size: str = "1.7B") -> ModelConfig:
 
 
 @dataclass
+class MixerSpec:
+    """One token mixer of a layered decoder: windowed attention over ``kv_heads`` shared key/value heads with a short
+    causal convolution (``conv`` taps) after the projections."""
+    heads: int
+    kv_heads: int
+    dim: int                       # query / key size per head
+    vdim: int                      # value size per head
+    conv: int                      # taps of the short convolution (1 = none)
+    window: int                    # keys a position sees, itself included
+    scale: float                   # score multiplier
+
+    @property
+    def channels(self) -> int:
+        return self.heads * self.dim + self.kv_heads * (self.dim + self.vdim)
+
+
+@dataclass
+class FeedForwardSpec:
+    kind: str                      # "dense" | "moe"
+    ff: int                        # inner size (of one expert for "moe")
+    experts: int = 0
+    top: int = 0
+    router_scale: float = 1.0
+
+
+@dataclass
+class LayerSpec:
+    type: str                      # which mixer ("attention")
+    mixer: MixerSpec
+    mlp: FeedForwardSpec | None
+
+
+@dataclass
+class BokenexConfig:
+    """``config.json`` of a Bokenex checkpoint: a decoder-only token model whose layers are listed one by one, each
+    with its own mixer sizes and feed-forward (dense, mixture of experts, or none).  Every size and every constant
+    that can differ between checkpoints is read here; nothing is assumed equal across layers."""
+    architecture: str
+    vocab: int
+    width: int
+    max_positions: int
+    norm_eps: float
+    residual_mult: float
+    layers: list
+
+    page_multiple = 64             # KV pages of this family may be any multiple of 64 tokens
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "BokenexConfig":
+        layers = []
+        for i, ld in enumerate(d["layers"]):
+            if ld["type"] != "attention":
+                raise ValueError(f"layer {i}: unknown mixer type {ld['type']!r}")
+            m = ld["mixer"]
+            mixer = MixerSpec(heads=int(m["heads"]), kv_heads=int(m["kv_heads"]), dim=int(m["dim"]), vdim=int(m["vdim"]),
+                              conv=int(m.get("conv", 1)), window=int(m["mask"]["size"]), scale=float(m["scale"]))
+            if mixer.heads % mixer.kv_heads:
+                raise ValueError(f"layer {i}: {mixer.heads} heads over {mixer.kv_heads} key/value heads")
+            f = ld.get("mlp")
+            mlp = None
+            if f is not None:
+                if f["kind"] == "dense":
+                    mlp = FeedForwardSpec("dense", int(f["ff"]))
+                elif f["kind"] == "moe":
+                    r = f["router"]
+                    mlp = FeedForwardSpec("moe", int(f["expert"]["ff"]), int(r["experts"]), int(r["top"]), float(r["scale"]))
+                else:
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {f['kind']!r}")
+            layers.append(LayerSpec(ld["type"], mixer, mlp))
+        return cls(architecture=d["architecture"], vocab=int(d["vocab"]), width=int(d["width"]),
+                   max_positions=int(d["max_positions"]), norm_eps=float(d["norm"]["eps"]),
+                   residual_mult=float(d["residual_mult"]), layers=layers)
+
+    @classmethod
+    def from_pretrained(cls, model_dir: str) -> "BokenexConfig":
+        with open(os.path.join(model_dir, "config.json")) as f:
+            return cls.from_dict(json.load(f))
+
+    def to_dict(self) -> dict:
+        out = []
+        for l in self.layers:
+            m = l.mixer
+            mlp = None
+            if l.mlp is not None and l.mlp.kind == "dense":
+                mlp = {"kind": "dense", "ff": l.mlp.ff}
+            elif l.mlp is not None:
+                mlp = {"kind": "moe", "expert": {"ff": l.mlp.ff},
+                       "router": {"experts": l.mlp.experts, "top": l.mlp.top, "scale": l.mlp.router_scale}}
+            out.append({"type": l.type, "mlp": mlp,
+                        "mixer": {"heads": m.heads, "kv_heads": m.kv_heads, "dim": m.dim, "vdim": m.vdim, "conv": m.conv,
+                                  "mask": {"size": m.window}, "scale": m.scale}})
+        return {"architecture": self.architecture, "vocab": self.vocab, "width": self.width,
+                "max_positions": self.max_positions, "norm": {"eps": self.norm_eps},
+                "residual_mult": self.residual_mult, "layers": out}
+
+
+def load_model_config(model_dir: str):
+    """Parse ``config.json`` with the configuration class its architecture is registered under."""
+    from .models.registry import resolve
+    with open(os.path.join(model_dir, "config.json")) as f:
+        d = json.load(f)
+    return resolve(d).config_cls.from_dict(d)
+
+
+@dataclass
 class Config:
     """Engine configuration; field names follow the reference's ``Config`` (config.py:41-66)."""
     model: str = ""
@@ -107,7 +212,7 @@ class Config:
     gpu_memory_utilization: float = 0.9
     tensor_parallel_size: int = 1
     enforce_eager: bool = False
-    hf_config: ModelConfig | None = None
+    hf_config: object | None = None            # ModelConfig, or the configuration class of a registered architecture
     eos: int = -1
     kvcache_block_size: int = 256
     num_kvcache_blocks: int = -1
@@ -118,10 +223,15 @@ class Config:
     rounding: int = 0                          # _native.ROUND_EAGER | ROUND_FUSED, see DESIGN.md
     graph_batch_sizes: list = field(default_factory=list)   # [] = reference's schedule
 
+    max_state_slots: int = 0                   # per-sequence recurrent / convolution state slots (0 = max_num_seqs)
+    dtype: str = "bfloat16"                    # activation and cache type: "bfloat16", or "float32" where a model has it
+
     def __post_init__(self):
-        assert self.kvcache_block_size % 256 == 0                      # config.py:60
-        assert self.tensor_parallel_size == 1, "replicas only: the hot path never shards a model (DESIGN.md)"
+        assert self.tensor_parallel_size == 1, "replicas only: the hot path never shards a model"
         assert self.max_num_batched_tokens >= self.max_model_len
         if self.hf_config is None and self.model:
             assert os.path.isdir(self.model), self.model               # config.py:59
-            self.hf_config = ModelConfig.from_pretrained(self.model)
+            self.hf_config = load_model_config(self.model)
+        # the reference's pages are multiples of 256 tokens (config.py:60); a model family may allow finer ones
+        assert self.kvcache_block_size % getattr(self.hf_config, "page_multiple", 256) == 0
+        assert self.dtype in ("bfloat16", "float32")

@@ -1,0 +1,460 @@
+// lm_ops.cu - element-wise and per-row kernels of token-id decoder models with a 32-bit residual stream:
+//   embedding + learned positions, RMS norm with one gain ("gain norm"), the residual update of a parallel layer fused
+//   with the next norm, the short causal convolution over time with its carried state fused with per-head q/k RMS norm
+//   and the paged K/V write, the squared-ReLU activation, and the sigmoid top-k router with its expert grouping.
+//
+// Activations are `T` = bf16 (serving) or float (the all-32-bit mode); the residual stream, every norm, the router and
+// all per-head constants are float in both.  Nothing allocates or synchronises; every launch is graph-capturable.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace b2 {
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+constexpr int ROW_THREADS = 256;
+
+// sum over the block; every thread gets the result.  `red` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();                       // red may still be read from a previous call
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nw ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+// h[row] = T(x[row] / sqrt(mean(x[row]^2) + eps) * gain) for the row this block owns (x just written by this block).
+template <typename T>
+__device__ __forceinline__ void gain_norm_tail(const float* xr, T* hr, int cols, float ssq, const float* gain, float eps,
+                                               float* red) {
+  const float tot = block_sum(ssq, red);
+  const float inv = 1.0f / sqrtf(tot / static_cast<float>(cols) + eps);
+  const float g = gain[0];
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) hr[c] = from_f<T>(xr[c] * inv * g);
+}
+
+// ------------------------------------------------------------------ embedding + learned position (+ first norm)
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS)
+embed_pos_norm_kernel(const int32_t* __restrict__ tokens, const int32_t* __restrict__ positions, const T* __restrict__ embed,
+                      const T* __restrict__ pos_table, float* __restrict__ x, T* __restrict__ h, const float* __restrict__ gain,
+                      int cols, int vocab, int max_pos, float eps) {
+  __shared__ float red[33];
+  const int row = blockIdx.x;
+  int tok = tokens[row], p = positions[row];
+  tok = min(max(tok, 0), vocab - 1);
+  p = min(max(p, 0), max_pos - 1);
+  const T* er = embed + static_cast<size_t>(tok) * cols;
+  const T* pr = pos_table + static_cast<size_t>(p) * cols;
+  float* xr = x + static_cast<size_t>(row) * cols;
+  float ssq = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    const float v = to_f(er[c]) + to_f(pr[c]);
+    xr[c] = v;
+    ssq += v * v;
+  }
+  if (h != nullptr) gain_norm_tail<T>(xr, h + static_cast<size_t>(row) * cols, cols, ssq, gain, eps, red);
+}
+
+// ------------------------------------------------------------------ residual update (+ next norm)
+// x[row] += mult * (a[row] + b[row] + sum_k w[row, k] * z[row * top + k]) with every term optional; then, if h is
+// given, h[row] = gain norm of the NEW x[row].  The expert terms are added in the order k = 0 .. top-1.
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS)
+residual_norm_kernel(float* __restrict__ x, const T* __restrict__ a, const T* __restrict__ b, const T* __restrict__ z,
+                     const float* __restrict__ zw, int top, float mult, T* __restrict__ h, const float* __restrict__ gain,
+                     int cols, float eps) {
+  __shared__ float red[33];
+  const size_t row = blockIdx.x;
+  float* xr = x + row * cols;
+  float ssq = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) {
+    float s = 0.f;
+    if (a != nullptr) s += to_f(a[row * cols + c]);
+    if (b != nullptr) s += to_f(b[row * cols + c]);
+    if (z != nullptr) {
+      float e = 0.f;
+      for (int k = 0; k < top; ++k) e += zw[row * top + k] * to_f(z[(row * top + k) * cols + c]);
+      s += e;
+    }
+    const float v = xr[c] + mult * s;
+    xr[c] = v;
+    ssq += v * v;
+  }
+  if (h != nullptr) gain_norm_tail<T>(xr, h + row * cols, cols, ssq, gain, eps, red);
+}
+
+// out[i] = gain norm of x[rows[i]] (the rows whose logits are wanted)
+template <typename T>
+__global__ void __launch_bounds__(ROW_THREADS)
+gather_gain_norm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows, T* __restrict__ out,
+                        const float* __restrict__ gain, int cols, float eps) {
+  __shared__ float red[33];
+  const size_t src = rows != nullptr ? rows[blockIdx.x] : blockIdx.x;
+  const float* xr = x + src * cols;
+  float ssq = 0.f;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) ssq += xr[c] * xr[c];
+  gain_norm_tail<T>(xr, out + static_cast<size_t>(blockIdx.x) * cols, cols, ssq, gain, eps, red);
+}
+
+// ------------------------------------------------------------------ squared ReLU, in place
+template <typename T>
+__global__ void relu_sq_kernel(T* __restrict__ y, size_t n) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const float v = fmaxf(to_f(y[i]), 0.f);
+    y[i] = from_f<T>(v * v);
+  }
+}
+
+// ------------------------------------------------------------------ short convolution + head norm + paged K/V write
+// One warp per (token, head slot); head slots are the H query heads, then the G key heads, then the G value heads of the
+// merged projection row u[n] = [q | k | v].  Tap j of the token at position p reads the projection of position
+// p - taps + 1 + j: from this step's rows when that position is in the step's portion, from the sequence's carried
+// state (its last taps - 1 projections, oldest first) when it came earlier, zero before the sequence's start.
+constexpr int CONV_WARPS = 8;
+constexpr int CONV_MAX_PER_LANE = 8;       // head sizes up to 256
+constexpr int CONV_MAX_TAPS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(CONV_WARPS * 32)
+conv_headnorm_kvwrite_kernel(const T* __restrict__ u, int64_t u_stride, const float* __restrict__ conv_w /* [C, taps] */,
+                             const T* __restrict__ state /* [slots, taps-1, C] */, const int32_t* __restrict__ tok_seq,
+                             const int32_t* __restrict__ positions, const int32_t* __restrict__ seq_start,
+                             const int32_t* __restrict__ seq_pos0, const int32_t* __restrict__ seq_slot,
+                             const int32_t* __restrict__ slot_mapping, const float* __restrict__ q_norm_w,
+                             const float* __restrict__ k_norm_w, T* __restrict__ q_out /* [n, H*d] */,
+                             T* __restrict__ k_cache /* [slots, G*d] */, T* __restrict__ v_cache /* [slots, G*dv] */,
+                             int n_tokens, int H, int G, int d, int dv, int taps, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * CONV_WARPS + (threadIdx.x >> 5);
+  const int heads = H + 2 * G;
+  if (item >= n_tokens * heads) return;
+  const int n = item / heads, hs = item % heads;
+  const int slot = slot_mapping[n];
+  if (slot < 0) return;                                  // padding row
+  const int C = H * d + G * d + G * dv;
+  int kind, head, width, c0;
+  if (hs < H) { kind = 0; head = hs; width = d; c0 = head * d; }
+  else if (hs < H + G) { kind = 1; head = hs - H; width = d; c0 = H * d + head * d; }
+  else { kind = 2; head = hs - H - G; width = dv; c0 = H * d + G * d + head * dv; }
+  const int b = tok_seq[n], p = positions[n];
+  const int pos0 = seq_pos0[b], start = seq_start[b], sslot = seq_slot[b];
+  const int R = taps - 1;
+  // where tap j comes from: a row of u (>= 0), a state entry (encoded as -2 - r) or nothing (-1)
+  int src[CONV_MAX_TAPS];
+#pragma unroll
+  for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+    src[j] = -1;
+    if (j < taps) {
+      const int pj = p - R + j;
+      if (pj >= pos0) src[j] = start + (pj - pos0);
+      else if (pj >= 0) src[j] = -2 - (pj - (pos0 - R));  // state entry r holds position pos0 - R + r
+    }
+  }
+  float y[CONV_MAX_PER_LANE];
+  float ssq = 0.f;
+#pragma unroll
+  for (int i = 0; i < CONV_MAX_PER_LANE; ++i) {
+    const int cc = lane + 32 * i;
+    y[i] = 0.f;
+    if (cc < width) {
+      const int c = c0 + cc;
+      float acc = 0.f;
+#pragma unroll
+      for (int j = 0; j < CONV_MAX_TAPS; ++j) {
+        if (j < taps && src[j] != -1) {
+          const float uv = src[j] >= 0 ? to_f(u[static_cast<int64_t>(src[j]) * u_stride + c])
+                                       : to_f(state[(static_cast<size_t>(sslot) * R + (-2 - src[j])) * C + c]);
+          acc += conv_w[c * taps + j] * uv;
+        }
+      }
+      y[i] = acc;
+      ssq += acc * acc;
+    }
+  }
+  if (kind != 2) {
+    // the projection and convolution outputs are activations: the norm reads them as stored in T
+    ssq = 0.f;
+#pragma unroll
+    for (int i = 0; i < CONV_MAX_PER_LANE; ++i) { y[i] = to_f(from_f<T>(y[i])); ssq += y[i] * y[i]; }
+    ssq = warp_sum(ssq);
+    const float inv = 1.0f / sqrtf(ssq / static_cast<float>(width) + eps);
+    const float* w = kind == 0 ? q_norm_w : k_norm_w;
+#pragma unroll
+    for (int i = 0; i < CONV_MAX_PER_LANE; ++i) {
+      const int cc = lane + 32 * i;
+      if (cc < width) y[i] = y[i] * inv * w[cc];
+    }
+  }
+  T* dst = kind == 0 ? q_out + static_cast<size_t>(n) * H * d + head * d
+         : kind == 1 ? k_cache + static_cast<size_t>(slot) * G * d + head * d
+                     : v_cache + static_cast<size_t>(slot) * G * dv + head * dv;
+#pragma unroll
+  for (int i = 0; i < CONV_MAX_PER_LANE; ++i) {
+    const int cc = lane + 32 * i;
+    if (cc < width) dst[cc] = from_f<T>(y[i]);
+  }
+}
+
+// The carried state after the step: entry r holds the projection of position end - R + r (end = pos0 + new tokens).
+// One thread per (sequence, channel) reads its old entries before it writes any, so the shift is safe in place.
+template <typename T>
+__global__ void conv_state_update_kernel(const T* __restrict__ u, int64_t u_stride, T* __restrict__ state,
+                                         const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_pos0,
+                                         const int32_t* __restrict__ seq_len, const int32_t* __restrict__ seq_slot,
+                                         int n_seqs, int C, int taps) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.y;
+  if (c >= C || b >= n_seqs) return;
+  const int len = seq_len[b];
+  if (len <= 0) return;                                  // padding row
+  const int R = taps - 1, pos0 = seq_pos0[b], start = seq_start[b];
+  T* st = state + static_cast<size_t>(seq_slot[b]) * R * C + c;
+  T old[CONV_MAX_TAPS];
+#pragma unroll
+  for (int r = 0; r < CONV_MAX_TAPS; ++r) if (r < R) old[r] = st[static_cast<size_t>(r) * C];
+  const int end = pos0 + len;
+#pragma unroll
+  for (int r = 0; r < CONV_MAX_TAPS; ++r) {
+    if (r < R) {
+      const int pj = end - R + r;
+      T v = from_f<T>(0.f);
+      if (pj >= pos0) v = u[static_cast<int64_t>(start + pj - pos0) * u_stride + c];
+      else if (pj >= 0) v = old[pj - (pos0 - R)];
+      st[static_cast<size_t>(r) * C] = v;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ sigmoid top-k router
+// One warp per token: logits over the experts in 32-bit, scores = sigmoid, the `top` largest (ties: the lower index),
+// weights = score / (sum of the chosen scores + 1e-20) * scale.
+constexpr int ROUTE_WARPS = 4;
+constexpr int ROUTE_MAX_EXPERTS = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router /* [E, cols] */, int32_t* __restrict__ top_idx,
+                 float* __restrict__ top_w, int n_tokens, int cols, int E, int top, float scale) {
+  __shared__ float score[ROUTE_WARPS][ROUTE_MAX_EXPERTS];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n = blockIdx.x * ROUTE_WARPS + warp;
+  if (n >= n_tokens) return;
+  const T* hr = h + static_cast<size_t>(n) * cols;
+  for (int e = 0; e < E; ++e) {
+    const float* wr = router + static_cast<size_t>(e) * cols;
+    float acc = 0.f;
+    for (int c = lane; c < cols; c += 32) acc += to_f(hr[c]) * wr[c];
+    acc = warp_sum(acc);
+    if (lane == 0) {
+      const float sc = 1.0f / (1.0f + expf(-acc));
+      score[warp][e] = sc >= 0.f ? sc : 0.f;             // a NaN input still yields valid expert ids
+    }
+  }
+  __syncwarp();
+  float sum = 0.f;
+  float chosen_s = 0.f;          // lane k keeps the k-th choice
+  int chosen_e = 0;
+  for (int k = 0; k < top; ++k) {
+    float best = -1.f;
+    int be = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float s = score[warp][e];
+      if (s > best) { best = s; be = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; }
+    }
+    if (lane == (k & 31)) { chosen_s = best; chosen_e = be; }
+    sum += best;
+    if (lane == 0) score[warp][be] = -2.f;
+    __syncwarp();
+  }
+  if (lane < top) {
+    top_idx[static_cast<size_t>(n) * top + lane] = chosen_e;
+    top_w[static_cast<size_t>(n) * top + lane] = chosen_s / (sum + 1e-20f) * scale;
+  }
+}
+
+// Group the (token, choice) pairs by expert: offsets[e] .. offsets[e+1] index `sorted_pair`, which holds pair ids
+// (token * top + choice).  One block; the order inside a group is arbitrary (no result depends on it).
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(const int32_t* __restrict__ top_idx, int32_t* __restrict__ offsets, int32_t* __restrict__ sorted_pair,
+                 int n_pairs, int E) {
+  __shared__ int count[ROUTE_MAX_EXPERTS + 1];
+  __shared__ int cursor[ROUTE_MAX_EXPERTS];
+  for (int e = threadIdx.x; e <= E; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&count[top_idx[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < E; ++e) { const int c = count[e]; cursor[e] = run; offsets[e] = run; run += c; }
+    offsets[E] = run;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) sorted_pair[atomicAdd(&cursor[top_idx[i]], 1)] = i;
+}
+
+template <typename T>
+static int launch_residual(float* x, const void* a, const void* b, const void* z, const float* zw, int top, float mult,
+                           void* h, const float* gain, int rows, int cols, float eps, cudaStream_t st) {
+  residual_norm_kernel<T><<<rows, ROW_THREADS, 0, st>>>(x, static_cast<const T*>(a), static_cast<const T*>(b),
+                                                         static_cast<const T*>(z), zw, top, mult, static_cast<T*>(h), gain,
+                                                         cols, eps);
+  return 0;
+}
+
+}  // namespace b2
+
+#define LM_DTYPE_OK(dt) ((dt) == B2TTS_DTYPE_BF16 || (dt) == B2TTS_DTYPE_F32)
+
+extern "C" int b2tts_embed_pos_norm(const int32_t* tokens, const int32_t* positions, const void* embed, const void* pos_table,
+                                    float* x, void* h, const float* gain, int rows, int cols, int vocab, int max_pos,
+                                    float eps, int dtype, void* stream) {
+  using namespace b2;
+  B2_REQUIRE(rows >= 0 && cols > 0 && vocab > 0 && max_pos > 0, B2TTS_EINVAL, "embed_pos_norm: rows=%d cols=%d", rows, cols);
+  B2_REQUIRE(LM_DTYPE_OK(dtype), B2TTS_EINVAL, "embed_pos_norm: dtype %d", dtype);
+  if (rows == 0) return B2TTS_OK;
+  B2_REQUIRE(tokens && positions && embed && pos_table && x && (!h || gain), B2TTS_EINVAL, "embed_pos_norm: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == B2TTS_DTYPE_BF16)
+    embed_pos_norm_kernel<__nv_bfloat16><<<rows, ROW_THREADS, 0, st>>>(tokens, positions, static_cast<const __nv_bfloat16*>(embed),
+        static_cast<const __nv_bfloat16*>(pos_table), x, static_cast<__nv_bfloat16*>(h), gain, cols, vocab, max_pos, eps);
+  else
+    embed_pos_norm_kernel<float><<<rows, ROW_THREADS, 0, st>>>(tokens, positions, static_cast<const float*>(embed),
+        static_cast<const float*>(pos_table), x, static_cast<float*>(h), gain, cols, vocab, max_pos, eps);
+  B2_CHECK_LAUNCH("embed_pos_norm");
+  return B2TTS_OK;
+}
+
+extern "C" int b2tts_residual_norm(float* x, const void* a, const void* b, const void* z, const float* zw, int top, float mult,
+                                   void* h, const float* gain, int rows, int cols, float eps, int dtype, void* stream) {
+  using namespace b2;
+  B2_REQUIRE(rows >= 0 && cols > 0 && top >= 0, B2TTS_EINVAL, "residual_norm: rows=%d cols=%d top=%d", rows, cols, top);
+  B2_REQUIRE(LM_DTYPE_OK(dtype), B2TTS_EINVAL, "residual_norm: dtype %d", dtype);
+  if (rows == 0) return B2TTS_OK;
+  B2_REQUIRE(x && (!h || gain) && (!z || (zw && top > 0)), B2TTS_EINVAL, "residual_norm: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == B2TTS_DTYPE_BF16) launch_residual<__nv_bfloat16>(x, a, b, z, zw, top, mult, h, gain, rows, cols, eps, st);
+  else launch_residual<float>(x, a, b, z, zw, top, mult, h, gain, rows, cols, eps, st);
+  B2_CHECK_LAUNCH("residual_norm");
+  return B2TTS_OK;
+}
+
+extern "C" int b2tts_gather_gain_norm(const float* x, const int32_t* rows_idx, void* out, const float* gain, int rows, int cols,
+                                      float eps, int dtype, void* stream) {
+  using namespace b2;
+  B2_REQUIRE(rows >= 0 && cols > 0, B2TTS_EINVAL, "gather_gain_norm: rows=%d cols=%d", rows, cols);
+  B2_REQUIRE(LM_DTYPE_OK(dtype), B2TTS_EINVAL, "gather_gain_norm: dtype %d", dtype);
+  if (rows == 0) return B2TTS_OK;
+  B2_REQUIRE(x && out && gain, B2TTS_EINVAL, "gather_gain_norm: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == B2TTS_DTYPE_BF16)
+    gather_gain_norm_kernel<__nv_bfloat16><<<rows, ROW_THREADS, 0, st>>>(x, rows_idx, static_cast<__nv_bfloat16*>(out), gain, cols, eps);
+  else
+    gather_gain_norm_kernel<float><<<rows, ROW_THREADS, 0, st>>>(x, rows_idx, static_cast<float*>(out), gain, cols, eps);
+  B2_CHECK_LAUNCH("gather_gain_norm");
+  return B2TTS_OK;
+}
+
+extern "C" int b2tts_relu_sq(void* y, int64_t n, int dtype, void* stream) {
+  using namespace b2;
+  B2_REQUIRE(n >= 0 && LM_DTYPE_OK(dtype), B2TTS_EINVAL, "relu_sq: n=%lld dtype=%d", static_cast<long long>(n), dtype);
+  if (n == 0) return B2TTS_OK;
+  B2_REQUIRE(y, B2TTS_EINVAL, "relu_sq: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int grid = static_cast<int>(std::min<int64_t>((n + 255) / 256, 148 * 16));
+  if (dtype == B2TTS_DTYPE_BF16) relu_sq_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<__nv_bfloat16*>(y), static_cast<size_t>(n));
+  else relu_sq_kernel<float><<<grid, 256, 0, st>>>(static_cast<float*>(y), static_cast<size_t>(n));
+  B2_CHECK_LAUNCH("relu_sq");
+  return B2TTS_OK;
+}
+
+extern "C" int b2tts_conv_headnorm_kvwrite(const void* u, int64_t u_stride, const float* conv_w, void* state,
+                                           const int32_t* tok_seq, const int32_t* positions, const int32_t* seq_start,
+                                           const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* seq_slot,
+                                           const int32_t* slot_mapping, const float* q_norm_w, const float* k_norm_w,
+                                           void* q_out, void* k_cache, void* v_cache, int n_tokens, int n_seqs, int heads,
+                                           int kv_heads, int dim, int vdim, int taps, float eps, int dtype, void* stream) {
+  using namespace b2;
+  B2_REQUIRE(n_tokens >= 0 && n_seqs >= 0 && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0, B2TTS_EINVAL,
+             "conv_headnorm_kvwrite: bad sizes");
+  B2_REQUIRE(taps >= 1 && taps <= CONV_MAX_TAPS, B2TTS_EUNSUPPORTED, "conv_headnorm_kvwrite: taps %d not in 1..%d", taps, CONV_MAX_TAPS);
+  B2_REQUIRE(dim <= 32 * CONV_MAX_PER_LANE && vdim <= 32 * CONV_MAX_PER_LANE, B2TTS_EUNSUPPORTED,
+             "conv_headnorm_kvwrite: head size above %d", 32 * CONV_MAX_PER_LANE);
+  B2_REQUIRE(LM_DTYPE_OK(dtype), B2TTS_EINVAL, "conv_headnorm_kvwrite: dtype %d", dtype);
+  if (n_tokens == 0 || n_seqs == 0) return B2TTS_OK;
+  B2_REQUIRE(u && conv_w && (state || taps == 1) && tok_seq && positions && seq_start && seq_pos0 && seq_len && seq_slot &&
+             slot_mapping && q_norm_w && k_norm_w && q_out && k_cache && v_cache, B2TTS_EINVAL, "conv_headnorm_kvwrite: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int items = n_tokens * (heads + 2 * kv_heads);
+  const int grid = (items + CONV_WARPS - 1) / CONV_WARPS;
+  const int C = heads * dim + kv_heads * dim + kv_heads * vdim;
+  if (dtype == B2TTS_DTYPE_BF16) {
+    using T = __nv_bfloat16;
+    conv_headnorm_kvwrite_kernel<T><<<grid, CONV_WARPS * 32, 0, st>>>(static_cast<const T*>(u), u_stride, conv_w, static_cast<const T*>(state),
+        tok_seq, positions, seq_start, seq_pos0, seq_slot, slot_mapping, q_norm_w, k_norm_w, static_cast<T*>(q_out),
+        static_cast<T*>(k_cache), static_cast<T*>(v_cache), n_tokens, heads, kv_heads, dim, vdim, taps, eps);
+    B2_CHECK_LAUNCH("conv_headnorm_kvwrite");
+    if (taps > 1) {
+      conv_state_update_kernel<T><<<dim3((C + 127) / 128, n_seqs), 128, 0, st>>>(static_cast<const T*>(u), u_stride, static_cast<T*>(state),
+          seq_start, seq_pos0, seq_len, seq_slot, n_seqs, C, taps);
+      B2_CHECK_LAUNCH("conv_state_update");
+    }
+  } else {
+    using T = float;
+    conv_headnorm_kvwrite_kernel<T><<<grid, CONV_WARPS * 32, 0, st>>>(static_cast<const T*>(u), u_stride, conv_w, static_cast<const T*>(state),
+        tok_seq, positions, seq_start, seq_pos0, seq_slot, slot_mapping, q_norm_w, k_norm_w, static_cast<T*>(q_out),
+        static_cast<T*>(k_cache), static_cast<T*>(v_cache), n_tokens, heads, kv_heads, dim, vdim, taps, eps);
+    B2_CHECK_LAUNCH("conv_headnorm_kvwrite");
+    if (taps > 1) {
+      conv_state_update_kernel<T><<<dim3((C + 127) / 128, n_seqs), 128, 0, st>>>(static_cast<const T*>(u), u_stride, static_cast<T*>(state),
+          seq_start, seq_pos0, seq_len, seq_slot, n_seqs, C, taps);
+      B2_CHECK_LAUNCH("conv_state_update");
+    }
+  }
+  return B2TTS_OK;
+}
+
+extern "C" int b2tts_moe_route(const void* h, const float* router, int32_t* top_idx, float* top_w, int32_t* offsets,
+                               int32_t* sorted_pair, int n_tokens, int cols, int experts, int top, float scale, int dtype,
+                               void* stream) {
+  using namespace b2;
+  B2_REQUIRE(n_tokens >= 0 && cols > 0 && experts > 0 && top > 0 && top <= experts, B2TTS_EINVAL, "moe_route: bad sizes");
+  B2_REQUIRE(experts <= ROUTE_MAX_EXPERTS && top <= 32, B2TTS_EUNSUPPORTED, "moe_route: experts %d > %d or top %d > 32", experts,
+             ROUTE_MAX_EXPERTS, top);
+  B2_REQUIRE(LM_DTYPE_OK(dtype), B2TTS_EINVAL, "moe_route: dtype %d", dtype);
+  B2_REQUIRE(offsets && sorted_pair, B2TTS_EINVAL, "moe_route: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n_tokens > 0) {
+    B2_REQUIRE(h && router && top_idx && top_w, B2TTS_EINVAL, "moe_route: null pointer");
+    const int grid = (n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS;
+    if (dtype == B2TTS_DTYPE_BF16)
+      moe_route_kernel<__nv_bfloat16><<<grid, ROUTE_WARPS * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(h), router, top_idx, top_w,
+                                                                          n_tokens, cols, experts, top, scale);
+    else
+      moe_route_kernel<float><<<grid, ROUTE_WARPS * 32, 0, st>>>(static_cast<const float*>(h), router, top_idx, top_w, n_tokens, cols,
+                                                                 experts, top, scale);
+    B2_CHECK_LAUNCH("moe_route");
+  }
+  moe_group_kernel<<<1, 1024, 0, st>>>(top_idx, offsets, sorted_pair, n_tokens * top, experts);
+  B2_CHECK_LAUNCH("moe_group");
+  return B2TTS_OK;
+}

@@ -45,3 +45,39 @@ class BlockManager:
     def may_append(self, seq: Sequence):
         if len(seq) % self.block_size == 1 and len(seq.block_table) < seq.num_blocks:
             seq.block_table.append(self._take())
+
+    # ---- growth by token count (prompts that arrive in portions: the table covers what has been computed so far)
+    def blocks_for(self, num_tokens: int) -> int:
+        return (num_tokens + self.block_size - 1) // self.block_size
+
+    def tokens_available(self, seq: Sequence) -> int:
+        """How many tokens the sequence can hold if it took every free page."""
+        return (len(seq.block_table) + len(self.free_block_ids)) * self.block_size
+
+    def extend(self, seq: Sequence, num_tokens: int):
+        """Grow the block table until it covers ``num_tokens`` tokens."""
+        need = self.blocks_for(num_tokens) - len(seq.block_table)
+        assert need <= len(self.free_block_ids), "extend() past the pool: check tokens_available() first"
+        for _ in range(need):
+            seq.block_table.append(self._take())
+
+
+class StateSlotPool:
+    """Slots of per-sequence state that is not paged (a short convolution's last inputs, a recurrence's carry): one
+    slot per live sequence, LIFO reuse like the pages.  A slot is NOT cleared when it changes owner: the kernels
+    treat what lies before position 0 as zero by position, not by content."""
+
+    def __init__(self, num_slots: int):
+        assert num_slots > 0
+        self.num_slots = num_slots
+        self.free: list[int] = list(range(num_slots - 1, -1, -1))
+
+    def available(self) -> int:
+        return len(self.free)
+
+    def take(self) -> int:
+        return self.free.pop()
+
+    def give(self, slot: int):
+        assert 0 <= slot < self.num_slots and slot not in self.free
+        self.free.append(slot)

@@ -111,8 +111,9 @@ class ModelRunner:
         self.stack_config = self.pick_stack_config(config.hf_config)
         self.max_blocks = (config.max_model_len + self.block_size - 1) // self.block_size
         self.max_bs = min(config.max_num_seqs, 512)
+        self.param_dtype = {"bfloat16": BF16, "float32": torch.float32}[getattr(config, "dtype", "bfloat16")]
         prev = torch.get_default_dtype()
-        torch.set_default_dtype(BF16)
+        torch.set_default_dtype(self.param_dtype)
         try:
             with torch.device(self.device):
                 self.model = self.build_model()

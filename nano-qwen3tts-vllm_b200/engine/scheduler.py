@@ -129,3 +129,72 @@ class TalkerScheduler(Scheduler):
 
 class PredictorScheduler(Scheduler):
     pass
+
+
+class ChunkScheduler(Scheduler):
+    """Continuous batching for token models whose prompts run in portions: one step carries the single pending token
+    of every decoding sequence BESIDE portions of prompts, up to ``max_num_batched_tokens`` tokens.  ``schedule``
+    returns ``[(sequence, tokens to run)]``; a sequence's block table grows as its portions are scheduled, and a
+    sequence is admitted when a state slot and the pages of its first portion are free.  Nothing is preempted: a
+    portion that does not fit is shortened, or waits for pages that finishing sequences give back."""
+
+    def __init__(self, config: Config):
+        super().__init__(config)
+        from .block_manager import StateSlotPool
+        self.state_slots = StateSlotPool(config.max_state_slots or config.max_num_seqs)
+
+    def is_finished(self):
+        return not self.waiting and not any(s.num_pending_tokens or not s.hold for s in self.running)
+
+    def _fit(self, seq: Sequence, budget: int) -> int:
+        n = min(seq.num_pending_tokens, budget)
+        room = self.block_manager.tokens_available(seq) - seq.num_cached_tokens
+        return max(0, min(n, room))
+
+    def schedule(self) -> list[tuple[Sequence, int]]:
+        picked, budget = [], self.max_num_batched_tokens
+        # decoding sequences first, so that a long prompt never starves them of the token budget
+        for decode_pass in (True, False):
+            for seq in self.running:
+                if (seq.num_pending_tokens == 1) != decode_pass or seq.num_pending_tokens == 0:
+                    continue
+                n = self._fit(seq, budget)
+                if n > 0:
+                    self.block_manager.extend(seq, seq.num_cached_tokens + n)
+                    picked.append((seq, n))
+                    budget -= n
+        while self.waiting and budget > 0 and len(self.running) < self.max_num_seqs and self.state_slots.available():
+            seq = self.waiting[0]
+            n = self._fit(seq, budget)
+            if n <= 0 and seq.num_pending_tokens > 0:
+                break
+            self.waiting.popleft()
+            seq.state_slot = self.state_slots.take()
+            seq.status = SequenceStatus.RUNNING
+            self.running.append(seq)
+            if n > 0:
+                self.block_manager.extend(seq, seq.num_cached_tokens + n)
+                picked.append((seq, n))
+                budget -= n
+        order = {id(s): i for i, s in enumerate(self.running)}
+        picked.sort(key=lambda it: order[id(it[0])])
+        return picked
+
+    def _release_state(self, seq: Sequence):
+        if seq.state_slot >= 0:
+            self.state_slots.give(seq.state_slot)
+            seq.state_slot = -1
+
+    def _finish(self, seq: Sequence):
+        self._release_state(seq)
+        super()._finish(seq)
+
+    def clear_request(self, request_id: str):
+        seq = self.request_id_to_seq.get(request_id)
+        if seq is not None:
+            self._release_state(seq)
+            seq.status = SequenceStatus.FINISHED
+        super().clear_request(request_id)
+
+    def preempt(self, seq: Sequence):
+        raise RuntimeError("ChunkScheduler never preempts")

@@ -42,6 +42,8 @@ class Sequence:
         self.top_k = sp.top_k
         self.generation_steps = 0
         self.last_hidden_state = None
+        self.state_slot = -1                   # slot of non-paged per-sequence state (engine/block_manager.py StateSlotPool)
+        self.hold = False                      # tokens are fed by the caller (replay / teacher forcing): nothing is sampled
 
     def __len__(self):
         return self.num_tokens
@@ -69,6 +71,20 @@ class Sequence:
     @property
     def last_block_num_tokens(self):
         return self.num_tokens - (self.num_blocks - 1) * self.block_size
+
+    @property
+    def num_pending_tokens(self):
+        """Tokens known but not yet run through the model (``num_cached_tokens`` counts those whose K/V are cached)."""
+        return self.num_tokens - self.num_cached_tokens
+
+    def feed(self, token_ids: list[int]):
+        """More tokens of a sequence whose text arrives in portions."""
+        self.token_ids.extend(token_ids)
+        self.num_tokens += len(token_ids)
+        if token_ids:
+            self.last_token = token_ids[-1]
+        if self.hold:
+            self.num_prompt_tokens = self.num_tokens
 
     def append_token(self, token_id: int, last_hidden_state=None):
         self.token_ids.append(token_id)

@@ -23,3 +23,10 @@ class SiluAndMul(nn.Module):
         x2 = x.view(-1, x.shape[-1])
         out = nat.silu_and_mul(x2[:, :inter], x2[:, inter:], self.rounding)
         return out.view(*x.shape[:-1], inter)
+
+
+class ReluSquared(nn.Module):
+    """max(x, 0)^2, in place (bf16 or float32)."""
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return nat.relu_sq_(x)

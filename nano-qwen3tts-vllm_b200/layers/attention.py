@@ -47,3 +47,30 @@ class Attention(nn.Module):
         if self.k_cache.numel() and self.v_cache.numel():
             store_kvcache(k, v, self.k_cache, self.v_cache, ctx.slot_mapping)
         return self.attend(q, k, v)
+
+
+class WindowSigmoidAttention(nn.Module):
+    """Sliding-window attention whose weights are sigmoids of the biased score, not a softmax:
+
+        w(i, j) = sigmoid(q_i . k_j * scale - r1_h * ln(1 + r2_h * (i - j)) + pb_h)    for 0 <= i - j < window
+
+    The cache holds this step's keys already (the convolution kernel wrote them), so prompt portions and decoded
+    tokens run through the same launch; the step's layout comes from the global Context.  ``r1``, ``r2``, ``pb`` are
+    per-head floats.  ``k_cache`` [pages, page, kv_heads * dim] and ``v_cache`` [pages, page, kv_heads * vdim] are bound
+    by the model runner."""
+
+    def __init__(self, heads: int, kv_heads: int, dim: int, vdim: int, window: int, scale: float):
+        super().__init__()
+        self.heads, self.kv_heads, self.dim, self.vdim, self.window, self.scale = heads, kv_heads, dim, vdim, window, scale
+        f32 = dict(dtype=torch.float32)
+        self.r1 = nn.Parameter(torch.zeros(heads, **f32), requires_grad=False)
+        self.r2 = nn.Parameter(torch.zeros(heads, **f32), requires_grad=False)
+        self.pb = nn.Parameter(torch.zeros(heads, **f32), requires_grad=False)
+        self.k_cache = self.v_cache = torch.tensor([])
+
+    def forward(self, q: torch.Tensor) -> torch.Tensor:
+        lay = get_context().step_layout
+        out = torch.empty(q.shape[0], self.heads * self.vdim, dtype=q.dtype, device=q.device)
+        nat.window_sigmoid_attn(q, self.k_cache, self.v_cache, out, lay, self.r1, self.r2, self.pb, self.heads,
+                                self.kv_heads, self.dim, self.vdim, self.k_cache.shape[1], self.window, self.scale)
+        return out

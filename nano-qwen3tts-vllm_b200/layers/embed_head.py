@@ -22,3 +22,21 @@ class ParallelLMHead(nn.Module):
             last = (ctx.cu_seqlens_q[1:] - 1).to(torch.int64)
             x = nat.gather_rows(x, last)
         return linear(x, self.weight)
+
+
+class TokenPositionEmbedding(nn.Module):
+    """Token embedding plus a learned, unscaled position vector, summed in float into a 32-bit residual stream; the
+    first layer's norm is applied in the same launch when ``norm`` is given."""
+
+    def __init__(self, vocab: int, max_positions: int, width: int):
+        super().__init__()
+        self.embed = nn.Parameter(torch.empty(vocab, width), requires_grad=False)
+        self.pos = nn.Parameter(torch.empty(max_positions, width), requires_grad=False)
+
+    def forward(self, tokens: torch.Tensor, positions: torch.Tensor, norm=None):
+        n, width = tokens.shape[0], self.embed.shape[1]
+        x = torch.empty(n, width, dtype=torch.float32, device=tokens.device)
+        h = torch.empty(n, width, dtype=self.embed.dtype, device=tokens.device) if norm is not None else None
+        nat.embed_pos_norm(tokens, positions, self.embed, self.pos, x, h, norm.gain() if norm is not None else None,
+                           norm.eps if norm is not None else 0.0)
+        return x, h

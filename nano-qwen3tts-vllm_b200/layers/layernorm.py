@@ -25,3 +25,21 @@ class Qwen3TTSRMSNorm(nn.Module):
         if residual is None:
             return self.rms_forward(x)
         return self.add_rms_forward(x, residual)
+
+
+class GainRMSNorm(nn.Module):
+    """RMS norm with ONE learned gain for all coordinates, over a 32-bit residual stream:
+    y = x / sqrt(mean(x^2) + eps) * g.  The gain is kept in float; the output takes the activation dtype.
+    In a model the norm rides in the kernel that produces x (``nat.embed_pos_norm`` / ``nat.residual_norm``);
+    ``forward`` is the stand-alone form, optionally over a subset of rows."""
+
+    def __init__(self, eps: float = 1e-6):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones((), dtype=torch.float32), requires_grad=False)
+
+    def gain(self) -> torch.Tensor:
+        return self.weight.view(1)
+
+    def forward(self, x: torch.Tensor, dtype: torch.dtype, rows: torch.Tensor | None = None) -> torch.Tensor:
+        return nat.gather_gain_norm(x, rows, self.gain(), self.eps, dtype)

@@ -100,7 +100,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
         raise RuntimeError("libb200tts: linear() needs CUDA tensors (there is no CPU path)")
     x2 = x.reshape(-1, x.shape[-1])
     m, n = x2.shape[0], weight.shape[0]
-    if native_ok(m, n, x2.shape[1]):
+    if x.dtype == torch.bfloat16 and native_ok(m, n, x2.shape[1]):
         ssq = _ssq_buffer(m, n, x2.shape[1], x.device) if want_ssq else None
         y = nat.gemm_bf16(x2, packed_weight(weight), n, bias=bias, out=out, pdl=PDL, ssq_out=ssq, prefetch=_pf(nxt),
                           **_norm_kw(norm))

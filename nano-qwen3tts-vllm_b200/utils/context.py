@@ -18,6 +18,7 @@ class Context:
     context_lens: torch.Tensor | None = None
     block_tables: torch.Tensor | None = None
     max_context_len: int = 0
+    step_layout: object | None = None      # mixed prompt-portion / decode batches: engine.step_layout.MixedStepLayout
 
 
 _CONTEXT = Context()
@@ -28,10 +29,10 @@ def get_context() -> Context:
 
 
 def set_context(is_prefill, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q=0, max_seqlen_k=0,
-                slot_mapping=None, context_lens=None, block_tables=None, max_context_len=0):
+                slot_mapping=None, context_lens=None, block_tables=None, max_context_len=0, step_layout=None):
     global _CONTEXT
     _CONTEXT = Context(is_prefill, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, slot_mapping,
-                       context_lens, block_tables, max_context_len)
+                       context_lens, block_tables, max_context_len, step_layout)
 
 
 def reset_context():
