@@ -143,7 +143,7 @@ class BokenexConfig:
     residual_mult: float
     layers: list
 
-    page_multiple = 64             # KV pages of this family may be any multiple of 64 tokens
+    page_multiple = 16             # KV pages of this family may be any multiple of 16 tokens
 
     @classmethod
     def from_dict(cls, d: dict) -> "BokenexConfig":

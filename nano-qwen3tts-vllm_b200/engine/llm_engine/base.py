@@ -21,7 +21,7 @@ class LLMEngine:
     def __init__(self, model: str | ModelConfig, state_dict: dict | None = None, **kwargs):
         names = {f.name for f in fields(Config)}
         cfg_kwargs = {k: v for k, v in kwargs.items() if k in names}          # llm_engine/base.py:18-20
-        if isinstance(model, ModelConfig):
+        if not isinstance(model, str):                                        # a parsed configuration object
             config = Config(model="", hf_config=model, **cfg_kwargs)
         else:
             config = Config(model, **cfg_kwargs)

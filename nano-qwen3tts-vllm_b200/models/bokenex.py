@@ -214,7 +214,7 @@ def random_state_dict(config: BokenexConfig, seed: int = 0) -> dict:
     D = config.width
 
     def rnd(*shape, std=1.0, mean=0.0):
-        return (mean + std * torch.randn(*shape, generator=g)).to(torch.bfloat16)
+        return (mean + std * torch.randn(shape, generator=g)).to(torch.bfloat16)
 
     sd = {"embed": rnd(config.vocab, D), "pos": rnd(config.max_positions, D, std=0.5), "final.norm": rnd(mean=1.0, std=0.05),
           "head": rnd(config.vocab, D, std=D ** -0.5)}

@@ -152,7 +152,7 @@ def random_weights(cfg: dict, seed: int = 0, dtype=torch.float64) -> dict:
     D = cfg["width"]
 
     def rnd(*shape, std=1.0, mean=0.0):
-        return (mean + std * torch.randn(*shape, generator=g)).to(torch.bfloat16).to(dtype)
+        return (mean + std * torch.randn(shape, generator=g)).to(torch.bfloat16).to(dtype)
 
     sd = {"embed": rnd(cfg["vocab"], D), "pos": rnd(cfg["max_positions"], D, std=0.5),
           "final.norm": rnd(std=0.1, mean=1.0), "head": rnd(cfg["vocab"], D, std=D ** -0.5)}
