@@ -54,6 +54,9 @@ def parse():
                     help="extra stream counts reported under other_workloads (BASELINE configs[1], [2], [4])")
     ap.add_argument("--no-icl", action="store_true", help="skip the BASELINE configs[3] leg (4k-token prompts, 8 streams)")
     ap.add_argument("--no-reference-kernels", action="store_true")
+    ap.add_argument("--lm", action="store_true",
+                    help="instead of the frame benchmark: prefill / decode throughput of the Bokenex decoder beside the talker "
+                         "stack at equal layer sizes, plus its kernels against their rooflines (bench_lm.py); one JSON line")
     return ap.parse_args()
 
 
@@ -476,6 +479,12 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device(device))
     barrier = (lambda: (dist.barrier(), torch.cuda.synchronize())) if dist else None
+
+    if a.lm:
+        import bench_lm
+        if rank == 0:
+            print(json.dumps(bench_lm.main(device)), flush=True)
+        return
 
     total_frames = a.steps + a.warmup + 8
     mc, talker, predictor = build_engines(a.model, a.streams, total_frames + 3 * a.e2e_steps + 8, device)

@@ -1,0 +1,308 @@
+"""``bench.py --lm``: prefill and decode throughput of the Bokenex decoder at layer sizes of a real model (random
+weights), beside the package's closest existing model - the Qwen3-TTS talker stack (GQA softmax attention + gated MLP)
+- with the same width, head layout, layer count and parameter count per layer.
+
+Per size and model:
+  prefill   tokens/s of one engine step over ``PREFILL_SEQS`` new prompts of ``PREFILL_LEN`` tokens (CUDA events around
+            the engine's own ``step()``: layout upload, all layers, last-token logits, sampling);
+  decode    tokens/s of the captured decode step for ``DECODE_SEQS`` sequences at a context of ``DECODE_CTX`` tokens
+            (CUDA-graph replays back to back: the device time of one step, no host in it).
+and, for the kernels that exist only in the new design, time and fraction of the measured roofline next to the like
+kernel of the talker (``kernels``).  Timing: 3+ warm-up runs, CUDA events on the launching stream; the working sets
+(weights + K/V of 64 sequences) are far above the 126 MB L2 for the decode steps, and an L2 flush precedes every timed
+kernel launch of the ``kernels`` section."""
+from __future__ import annotations
+
+import json
+import os
+import time
+
+PREFILL_SEQS, PREFILL_LEN = 4, 2048
+DECODE_SEQS, DECODE_CTX = 64, 1100
+WINDOW, TAPS, LAYERS = 1024, 4, 4
+PAGE = 256
+
+SIZES = {
+    # name: width, heads, kv_heads, head size, talker intermediate (gated: 3 matrices) -> dense ff with the same parameters
+    "w1024": dict(width=1024, heads=16, kv_heads=8, dim=128, inter=3072),
+    "w2048": dict(width=2048, heads=16, kv_heads=8, dim=128, inter=6144),
+}
+
+
+def _peaks():
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p["hbm_gbs"], p["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def bokenex_config(s: dict, moe: bool):
+    from nano_qwen3tts_vllm_b200.config import BokenexConfig
+    ff = s["inter"] * 3 // 2
+    mlp = {"kind": "dense", "ff": ff} if not moe else \
+        {"kind": "moe", "expert": {"ff": ff // 2}, "router": {"experts": 16, "top": 2, "scale": 1.0}}
+    layer = {"type": "attention", "mlp": mlp,
+             "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "conv": TAPS,
+                       "mask": {"size": WINDOW}, "scale": s["dim"] ** -0.5}}
+    return BokenexConfig.from_dict({"architecture": "Bokenex", "vocab": 3072, "width": s["width"], "max_positions": 4096,
+                                    "norm": {"eps": 1e-6}, "residual_mult": 0.5, "layers": [layer] * LAYERS})
+
+
+def _events(fn, iters, warm=3):
+    import torch
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def bench_bokenex(s: dict, moe: bool, device: str) -> dict:
+    import torch
+    from nano_qwen3tts_vllm_b200.engine.llm_engine.lm_engine import CausalLMEngine
+    from nano_qwen3tts_vllm_b200.sampling_params import SamplingParams
+    cfg = bokenex_config(s, moe)
+    pages = DECODE_SEQS * ((DECODE_CTX + 64 + PAGE - 1) // PAGE) + PREFILL_SEQS * (PREFILL_LEN // PAGE + 1)
+    eng = CausalLMEngine(cfg, state_dict="random:7", kvcache_block_size=PAGE, num_kvcache_blocks=pages,
+                         max_num_seqs=DECODE_SEQS + PREFILL_SEQS, max_model_len=4096, max_num_batched_tokens=16384,
+                         graph_batch_sizes=[DECODE_SEQS], device=device)
+    g = torch.Generator().manual_seed(0)
+    sp = SamplingParams(temperature=1.0, max_tokens=1 << 20, ignore_eos=True)
+    prompt = lambda n: torch.randint(0, cfg.vocab, (n,), generator=g).tolist()
+    out = {}
+    # prefill: new prompts every run, given back afterwards
+    times = []
+    for it in range(6):
+        ids = [f"p{it}_{i}" for i in range(PREFILL_SEQS)]
+        for i in ids:
+            eng.add_request(prompt(PREFILL_LEN), sp, request_id=i, hold=True)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        eng.step(want={i: [PREFILL_LEN - 1] for i in ids})
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+        for i in ids:
+            eng.clear_request(i)
+    ms = sorted(times[3:])[len(times[3:]) // 2]
+    out["prefill_ms"] = round(ms, 3)
+    out["prefill_tok_s"] = round(PREFILL_SEQS * PREFILL_LEN / ms * 1e3)
+    # decode: fill the contexts, one real decode step, then the captured step back to back
+    for i in range(DECODE_SEQS):
+        eng.add_request(prompt(DECODE_CTX), sp, request_id=f"d{i}")
+    while any(s_.num_pending_tokens > 1 for s_ in eng.scheduler.running) or eng.scheduler.waiting:
+        eng.step()
+    eng.step()
+    r = eng.model_runner
+    assert DECODE_SEQS in r.graphs
+    r.layout.set_decode_shape(DECODE_SEQS)
+    ms = _events(r.graphs[DECODE_SEQS].replay, 30)
+    out["decode_ms"] = round(ms, 4)
+    out["decode_tok_s"] = round(DECODE_SEQS / ms * 1e3)
+    eng.exit()
+    return out
+
+
+def bench_talker(s: dict, device: str) -> dict:
+    import torch
+    from nano_qwen3tts_vllm_b200.config import ModelConfig, StackConfig
+    from nano_qwen3tts_vllm_b200.llm import TalkerLLM
+    from nano_qwen3tts_vllm_b200.sampling_params import SamplingParams
+    stack = StackConfig(hidden_size=s["width"], intermediate_size=s["inter"], num_hidden_layers=LAYERS,
+                        num_attention_heads=s["heads"], num_key_value_heads=s["kv_heads"], head_dim=s["dim"], vocab_size=3072,
+                        rope_scaling={"mrope_section": [24, 20, 20], "interleaved": True})
+    mc = ModelConfig(stack, StackConfig(hidden_size=256, intermediate_size=512, num_hidden_layers=1, vocab_size=2048))
+    pages = DECODE_SEQS * ((DECODE_CTX + 64 + PAGE - 1) // PAGE) + PREFILL_SEQS * (PREFILL_LEN // PAGE + 1)
+    eng = TalkerLLM(mc, state_dict="random:7", num_kvcache_blocks=pages, max_num_seqs=DECODE_SEQS + PREFILL_SEQS,
+                    max_model_len=4096, max_num_batched_tokens=16384, graph_batch_sizes=[DECODE_SEQS], device=device)
+    sp = SamplingParams(temperature=1.0, max_tokens=1 << 20, ignore_eos=True)
+    g = torch.Generator().manual_seed(0)
+    emb = lambda n: (torch.randn(1, n, s["width"], generator=g) * 0.5).to(torch.bfloat16)
+    out, times = {}, []
+    for it in range(6):
+        ids = [f"p{it}_{i}" for i in range(PREFILL_SEQS)]
+        for i in ids:
+            eng.add_request([emb(PREFILL_LEN)], sp, request_id=i)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        eng.step()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+        for i in ids:
+            eng.clear_request(i)
+    ms = sorted(times[3:])[len(times[3:]) // 2]
+    out["prefill_ms"] = round(ms, 3)
+    out["prefill_tok_s"] = round(PREFILL_SEQS * PREFILL_LEN / ms * 1e3)
+    ids = [f"d{i}" for i in range(DECODE_SEQS)]
+    for i in ids:
+        eng.add_request([emb(DECODE_CTX)], sp, request_id=i)
+    eng.step()
+    eng.add_requests(torch.randn(DECODE_SEQS, 1, s["width"], generator=g).to(torch.bfloat16), sp, ids)
+    eng.step()
+    r = eng.model_runner
+    assert DECODE_SEQS in r.graphs
+    r.set_decode_context(DECODE_SEQS)
+    ms = _events(r.graphs[DECODE_SEQS].replay, 30)
+    out["decode_ms"] = round(ms, 4)
+    out["decode_tok_s"] = round(DECODE_SEQS / ms * 1e3)
+    eng.exit()
+    return out
+
+
+def bench_kernels(device: str) -> dict:
+    """The new design's own kernels at the w2048 layer shape, each after an L2 flush, with the fraction of the measured
+    roofline (HBM copy bandwidth for the streaming kernels, cuBLAS bf16 for the contractions) and the like kernel of
+    the talker measured the same way."""
+    import torch
+    import nano_qwen3tts_vllm_b200._native as nat
+    hbm, tflops, how = _peaks()
+    dev = torch.device(device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    BF = torch.bfloat16
+
+    def timed(fn, iters=5):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return sorted(ts)[len(ts) // 2]
+
+    class Lay:
+        pass
+
+    def layout(n_seqs, cached, new, pages_per_seq):
+        lay = Lay()
+        i32 = dict(dtype=torch.int32, device=dev)
+        lay.n_seqs, lay.max_new, lay.n_tokens = n_seqs, new, n_seqs * new
+        lay.seq_start = torch.arange(n_seqs, **i32) * new
+        lay.seq_pos0 = torch.full((n_seqs,), cached, **i32)
+        lay.seq_len = torch.full((n_seqs,), new, **i32)
+        lay.seq_slot = torch.arange(n_seqs, **i32)
+        lay.block_tables = torch.arange(n_seqs * pages_per_seq, **i32).view(n_seqs, pages_per_seq).contiguous()
+        pos = (torch.arange(new, **i32) + cached).repeat(n_seqs)
+        lay.positions = pos
+        lay.tok_seq = torch.arange(n_seqs, **i32).repeat_interleave(new)
+        lay.slot_mapping = (lay.tok_seq * pages_per_seq * PAGE + pos).to(torch.int32)
+        return lay
+
+    H, G, d, D = 16, 8, 128, 2048
+    res = {"peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": how}}
+    r1 = torch.full((H,), 0.5, device=dev)
+    r2 = torch.full((H,), 0.5, device=dev)
+    pb = torch.full((H,), -3.0, device=dev)
+
+    def entry(ms, bytes_=None, flops=None):
+        e = {"us": round(ms * 1e3, 1)}
+        if bytes_ is not None:
+            e["gbs"] = round(bytes_ / ms / 1e6, 1)
+            e["frac_hbm"] = round(bytes_ / ms / 1e6 / hbm, 3)
+        if flops is not None:
+            e["tflops"] = round(flops / ms / 1e9, 1)
+            e["frac_tensor"] = round(flops / ms / 1e9 / tflops, 4)
+        return e
+
+    # ---- attention, decode: 64 sequences at context 1100 (window 1024)
+    pps = (DECODE_CTX + PAGE) // PAGE + 1
+    lay = layout(DECODE_SEQS, DECODE_CTX, 1, pps)
+    kc = torch.randn(DECODE_SEQS * pps, PAGE, G * d, device=dev).to(BF)
+    vc = torch.randn(DECODE_SEQS * pps, PAGE, G * d, device=dev).to(BF)
+    q = torch.randn(DECODE_SEQS, H * d, device=dev).to(BF)
+    o = torch.empty_like(q)
+    ms = timed(lambda: nat.window_sigmoid_attn(q, kc, vc, o, lay, r1, r2, pb, H, G, d, d, PAGE, WINDOW, d ** -0.5))
+    res["window_sigmoid_attn decode 64x1100"] = entry(ms, bytes_=DECODE_SEQS * WINDOW * G * d * 2 * 2)
+    ctx = torch.full((DECODE_SEQS,), DECODE_CTX + 1, dtype=torch.int32, device=dev)
+    ws = torch.empty(nat.paged_attn_decode_workspace_bytes(DECODE_SEQS, H, d, pps * PAGE), dtype=torch.uint8, device=dev)
+    kc4, vc4 = kc.view(-1, PAGE, G, d), vc.view(-1, PAGE, G, d)
+    ms = timed(lambda: nat.paged_attn_decode(q.view(-1, H, d), kc4, vc4, lay.block_tables, ctx, d ** -0.5, pps * PAGE, workspace=ws))
+    res["paged_attn_decode (talker) 64x1100"] = entry(ms, bytes_=DECODE_SEQS * (DECODE_CTX + 1) * G * d * 2 * 2)
+    # ---- attention, prefill: 4 x 2048 tokens
+    pps = PREFILL_LEN // PAGE
+    lay = layout(PREFILL_SEQS, 0, PREFILL_LEN, pps)
+    n = PREFILL_SEQS * PREFILL_LEN
+    q = torch.randn(n, H * d, device=dev).to(BF)
+    o = torch.empty_like(q)
+    ms = timed(lambda: nat.window_sigmoid_attn(q, kc, vc, o, lay, r1, r2, pb, H, G, d, d, PAGE, WINDOW, d ** -0.5))
+    pairs = PREFILL_SEQS * sum(min(i + 1, WINDOW) for i in range(PREFILL_LEN))
+    res["window_sigmoid_attn prefill 4x2048"] = entry(ms, flops=pairs * H * d * 4)
+    k = torch.randn(n, G, d, device=dev).to(BF)
+    v = torch.randn(n, G, d, device=dev).to(BF)
+    cu = (torch.arange(PREFILL_SEQS + 1, dtype=torch.int32, device=dev) * PREFILL_LEN).contiguous()
+    ms = timed(lambda: nat.varlen_attn_prefill(q.view(n, H, d), k, v, cu, cu, PREFILL_LEN, PREFILL_LEN, d ** -0.5))
+    res["prefill_attn_tc (talker, full causal) 4x2048"] = entry(ms, flops=PREFILL_SEQS * PREFILL_LEN * (PREFILL_LEN + 1) / 2 * H * d * 4)
+    # ---- convolution + head norm + K/V write against head norm + rotation + K/V write
+    C = H * d + 2 * G * d
+    u = torch.randn(n, C, device=dev).to(BF)
+    cw = torch.randn(C, TAPS, device=dev)
+    st = torch.zeros(PREFILL_SEQS, TAPS - 1, C, dtype=BF, device=dev)
+    nw = torch.ones(d, device=dev)
+    qo = torch.empty(n, H * d, dtype=BF, device=dev)
+    ms = timed(lambda: nat.conv_headnorm_kvwrite(u, cw, st, lay, nw, nw, qo, kc, vc, H, G, d, d, TAPS, 1e-6))
+    res["conv_headnorm_kvwrite 8192 tokens"] = entry(ms, bytes_=n * (C + C) * 2)
+    pos64 = lay.positions.to(torch.int64)
+    inv = (1e6 ** (-torch.arange(0, d, 2, device=dev).float() / d)).contiguous()
+    nwb = nw.to(BF)
+    ms = timed(lambda: nat.qknorm_rope_kvwrite(u[:, :H * d].view(n, H, d), u[:, H * d:H * d + G * d].view(n, G, d),
+                                               u[:, H * d + G * d:].view(n, G, d), nwb, nwb, 1e-6, pos64, inv,
+                                               slot_mapping=lay.slot_mapping, k_cache=kc4, v_cache=vc4, want_k_out=False))
+    res["qknorm_rope_kvwrite (talker) 8192 tokens"] = entry(ms, bytes_=n * (C + C) * 2)
+    # ---- residual update + next norm against add + RMS norm
+    x = torch.randn(n, D, device=dev)
+    a_, b_ = torch.randn(n, D, device=dev).to(BF), torch.randn(n, D, device=dev).to(BF)
+    h = torch.empty(n, D, dtype=BF, device=dev)
+    gain = torch.ones(1, device=dev)
+    ms = timed(lambda: nat.residual_norm(x, a_, b_, None, None, 0.5, h, gain, 1e-6, BF))
+    res["residual_norm 8192x2048"] = entry(ms, bytes_=n * D * (4 + 4 + 2 + 2 + 2))
+    wv = torch.ones(D, dtype=BF, device=dev)
+    ms = timed(lambda: nat.add_rmsnorm(a_, b_, wv, 1e-6, 0, round_sum_first=False))
+    res["add_rmsnorm (talker) 8192x2048"] = entry(ms, bytes_=n * D * 2 * 4)
+    # ---- experts: grouped GEMM against the dense library GEMM of the same FLOPs
+    E, top, ff = 16, 2, 4608
+    from nano_qwen3tts_vllm_b200.layers.moe import SigmoidTopKMoE
+    moe = SigmoidTopKMoE(D, ff, E, top, 1.0).to(dev)
+    moe.router.normal_(0, D ** -0.5)
+    moe.up.data = (torch.randn(E, ff, D, device=dev) * D ** -0.5).to(BF)
+    moe.down.data = (torch.randn(E, D, ff, device=dev) * ff ** -0.5).to(BF)
+    hh = torch.randn(n, D, device=dev).to(BF)
+    ms = timed(lambda: moe(hh), iters=3)
+    res["moe (route + 2 grouped GEMMs) 8192 tokens"] = entry(ms, flops=n * top * ff * D * 4)
+    wd = (torch.randn(top * ff, D, device=dev) * 0.02).to(BF)
+    ms = timed(lambda: torch.nn.functional.linear(hh, wd))
+    res["dense GEMM of one projection's FLOPs (cuBLAS)"] = entry(ms, flops=n * top * ff * D * 2)
+    return res
+
+
+def main(device: str = "cuda:0") -> dict:
+    import torch
+    t0 = time.time()
+    out = {"metric": "lm_prefill_decode_throughput", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights)",
+           "config": {"prefill": f"{PREFILL_SEQS}x{PREFILL_LEN} tokens per step", "decode": f"{DECODE_SEQS} sequences at context {DECODE_CTX}",
+                      "layers": LAYERS, "window": WINDOW, "conv_taps": TAPS, "page": PAGE}, "sizes": {}}
+    for name, s in SIZES.items():
+        row = {"bokenex_dense": bench_bokenex(s, False, device), "bokenex_moe16top2": bench_bokenex(s, True, device),
+               "talker_stack": bench_talker(s, device)}
+        out["sizes"][name] = row
+        torch.cuda.empty_cache()
+    out["kernels"] = bench_kernels(device)
+    out["seconds"] = round(time.time() - t0, 1)
+    return out
+
+
+if __name__ == "__main__":
+    print(json.dumps(main()))
