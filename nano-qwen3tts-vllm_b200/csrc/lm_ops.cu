@@ -209,6 +209,113 @@ conv_headnorm_kvwrite_kernel(const T* __restrict__ u, int64_t u_stride, const fl
   }
 }
 
+// The same with four adjacent channels per lane (8- or 16-byte loads and stores) for head sizes that are multiples of 4.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  __device__ static void load(const float* p, float* f) { const float4 r = *reinterpret_cast<const float4*>(p); f[0] = r.x; f[1] = r.y; f[2] = r.z; f[3] = r.w; }
+  __device__ static void store(float* p, const float* f) { *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]); }
+};
+template <> struct Vec4<__nv_bfloat16> {
+  __device__ static void load(const __nv_bfloat16* p, float* f) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    f[0] = bf16lo(r.x); f[1] = bf16hi(r.x); f[2] = bf16lo(r.y); f[3] = bf16hi(r.y);
+  }
+  __device__ static void store(__nv_bfloat16* p, const float* f) { *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3])); }
+};
+constexpr int CONV4_CHUNKS = 2;            // head sizes up to 256
+
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(CONV_WARPS * 32)
+conv_headnorm_kvwrite_vec4_kernel(const T* __restrict__ u, int64_t u_stride, const float* __restrict__ conv_w,
+                                  const T* __restrict__ state, const int32_t* __restrict__ tok_seq,
+                                  const int32_t* __restrict__ positions, const int32_t* __restrict__ seq_start,
+                                  const int32_t* __restrict__ seq_pos0, const int32_t* __restrict__ seq_slot,
+                                  const int32_t* __restrict__ slot_mapping, const float* __restrict__ q_norm_w,
+                                  const float* __restrict__ k_norm_w, T* __restrict__ q_out, T* __restrict__ k_cache,
+                                  T* __restrict__ v_cache, int n_tokens, int H, int G, int d, int dv, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * CONV_WARPS + (threadIdx.x >> 5);
+  const int heads = H + 2 * G;
+  if (item >= n_tokens * heads) return;
+  const int n = item / heads, hs = item % heads;
+  const int slot = slot_mapping[n];
+  if (slot < 0) return;
+  const int C = H * d + G * d + G * dv;
+  int kind, head, width, c0;
+  if (hs < H) { kind = 0; head = hs; width = d; c0 = head * d; }
+  else if (hs < H + G) { kind = 1; head = hs - H; width = d; c0 = H * d + head * d; }
+  else { kind = 2; head = hs - H - G; width = dv; c0 = H * d + G * d + head * dv; }
+  const int b = tok_seq[n], p = positions[n];
+  const int pos0 = seq_pos0[b], start = seq_start[b], sslot = seq_slot[b];
+  constexpr int R = TAPS - 1;
+  const T* src[TAPS];                      // row of tap j (nullptr: before the sequence's start)
+#pragma unroll
+  for (int j = 0; j < TAPS; ++j) {
+    const int pj = p - R + j;
+    src[j] = nullptr;
+    if (pj >= pos0) src[j] = u + static_cast<int64_t>(start + pj - pos0) * u_stride;
+    else if (pj >= 0) src[j] = state + (static_cast<size_t>(sslot) * R + (pj - (pos0 - R))) * C;
+  }
+  float y[CONV4_CHUNKS][4];
+  float ssq = 0.f;
+#pragma unroll
+  for (int i = 0; i < CONV4_CHUNKS; ++i) {
+    const int cc = (lane + 32 * i) * 4;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) y[i][e] = 0.f;
+    if (cc < width) {
+      const int c = c0 + cc;
+      float w[4][TAPS];
+      if constexpr (TAPS == 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float4 r = *reinterpret_cast<const float4*>(conv_w + static_cast<size_t>(c + e) * TAPS);
+          w[e][0] = r.x; w[e][1] = r.y; w[e][2] = r.z; w[e][3] = r.w;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+#pragma unroll
+          for (int j = 0; j < TAPS; ++j) w[e][j] = conv_w[static_cast<size_t>(c + e) * TAPS + j];
+      }
+#pragma unroll
+      for (int j = 0; j < TAPS; ++j) {
+        if (src[j] != nullptr) {
+          float uv[4];
+          Vec4<T>::load(src[j] + c, uv);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) y[i][e] = fmaf(w[e][j], uv[e], y[i][e]);
+        }
+      }
+    }
+  }
+  if (kind != 2) {
+#pragma unroll
+    for (int i = 0; i < CONV4_CHUNKS; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { y[i][e] = to_f(from_f<T>(y[i][e])); ssq += y[i][e] * y[i][e]; }
+    ssq = warp_sum(ssq);
+    const float inv = 1.0f / sqrtf(ssq / static_cast<float>(width) + eps);
+    const float* nw = kind == 0 ? q_norm_w : k_norm_w;
+#pragma unroll
+    for (int i = 0; i < CONV4_CHUNKS; ++i) {
+      const int cc = (lane + 32 * i) * 4;
+      if (cc < width) {
+        const float4 g4 = *reinterpret_cast<const float4*>(nw + cc);
+        y[i][0] *= inv * g4.x; y[i][1] *= inv * g4.y; y[i][2] *= inv * g4.z; y[i][3] *= inv * g4.w;
+      }
+    }
+  }
+  T* dst = kind == 0 ? q_out + static_cast<size_t>(n) * H * d + head * d
+         : kind == 1 ? k_cache + static_cast<size_t>(slot) * G * d + head * d
+                     : v_cache + static_cast<size_t>(slot) * G * dv + head * dv;
+#pragma unroll
+  for (int i = 0; i < CONV4_CHUNKS; ++i) {
+    const int cc = (lane + 32 * i) * 4;
+    if (cc < width) Vec4<T>::store(dst + cc, y[i]);
+  }
+}
+
 // The carried state after the step: entry r holds the projection of position end - R + r (end = pos0 + new tokens).
 // One thread per (sequence, channel) reads its old entries before it writes any, so the shift is safe in place.
 template <typename T>
@@ -237,6 +344,18 @@ __global__ void conv_state_update_kernel(const T* __restrict__ u, int64_t u_stri
       st[static_cast<size_t>(r) * C] = v;
     }
   }
+}
+
+// ------------------------------------------------------------------ row gather / scatter by an index list
+// gather:  out[i] = in[idx[i] / div]      scatter:  out[idx[i]] = in[i]        (rows of `cols` elements)
+template <typename T>
+__global__ void permute_rows_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t* __restrict__ idx, int cols, int div,
+                                    int scatter) {
+  const size_t i = blockIdx.x;
+  const size_t j = static_cast<size_t>(idx[i]) / div;
+  const T* src = in + (scatter ? i : j) * cols;
+  T* dst = out + (scatter ? j : i) * cols;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) dst[c] = src[c];
 }
 
 // ------------------------------------------------------------------ sigmoid top-k router
@@ -310,6 +429,29 @@ moe_group_kernel(const int32_t* __restrict__ top_idx, int32_t* __restrict__ offs
   }
   __syncthreads();
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) sorted_pair[atomicAdd(&cursor[top_idx[i]], 1)] = i;
+}
+
+template <typename T>
+static void launch_conv(bool vec4, int grid, cudaStream_t st, const void* u, int64_t u_stride, const float* conv_w, void* state,
+                        const int32_t* tok_seq, const int32_t* positions, const int32_t* seq_start, const int32_t* seq_pos0,
+                        const int32_t* seq_len, const int32_t* seq_slot, const int32_t* slot_mapping, const float* q_norm_w,
+                        const float* k_norm_w, void* q_out, void* k_cache, void* v_cache, int n_tokens, int n_seqs, int H, int G, int d,
+                        int dv, int taps, float eps, int C) {
+#define CONV4_GO(TP) conv_headnorm_kvwrite_vec4_kernel<T, TP><<<grid, CONV_WARPS * 32, 0, st>>>(static_cast<const T*>(u), u_stride, conv_w, \
+      static_cast<const T*>(state), tok_seq, positions, seq_start, seq_pos0, seq_slot, slot_mapping, q_norm_w, k_norm_w, \
+      static_cast<T*>(q_out), static_cast<T*>(k_cache), static_cast<T*>(v_cache), n_tokens, H, G, d, dv, eps)
+  if (vec4 && taps == 4) CONV4_GO(4);
+  else if (vec4 && taps == 3) CONV4_GO(3);
+  else if (vec4 && taps == 2) CONV4_GO(2);
+  else if (vec4 && taps == 1) CONV4_GO(1);
+  else
+    conv_headnorm_kvwrite_kernel<T><<<grid, CONV_WARPS * 32, 0, st>>>(static_cast<const T*>(u), u_stride, conv_w, static_cast<const T*>(state),
+        tok_seq, positions, seq_start, seq_pos0, seq_slot, slot_mapping, q_norm_w, k_norm_w, static_cast<T*>(q_out),
+        static_cast<T*>(k_cache), static_cast<T*>(v_cache), n_tokens, H, G, d, dv, taps, eps);
+#undef CONV4_GO
+  if (taps > 1)
+    conv_state_update_kernel<T><<<dim3((C + 127) / 128, n_seqs), 128, 0, st>>>(static_cast<const T*>(u), u_stride, static_cast<T*>(state),
+        seq_start, seq_pos0, seq_len, seq_slot, n_seqs, C, taps);
 }
 
 template <typename T>
@@ -407,29 +549,17 @@ extern "C" int b2tts_conv_headnorm_kvwrite(const void* u, int64_t u_stride, cons
   const int items = n_tokens * (heads + 2 * kv_heads);
   const int grid = (items + CONV_WARPS - 1) / CONV_WARPS;
   const int C = heads * dim + kv_heads * dim + kv_heads * vdim;
-  if (dtype == B2TTS_DTYPE_BF16) {
-    using T = __nv_bfloat16;
-    conv_headnorm_kvwrite_kernel<T><<<grid, CONV_WARPS * 32, 0, st>>>(static_cast<const T*>(u), u_stride, conv_w, static_cast<const T*>(state),
-        tok_seq, positions, seq_start, seq_pos0, seq_slot, slot_mapping, q_norm_w, k_norm_w, static_cast<T*>(q_out),
-        static_cast<T*>(k_cache), static_cast<T*>(v_cache), n_tokens, heads, kv_heads, dim, vdim, taps, eps);
-    B2_CHECK_LAUNCH("conv_headnorm_kvwrite");
-    if (taps > 1) {
-      conv_state_update_kernel<T><<<dim3((C + 127) / 128, n_seqs), 128, 0, st>>>(static_cast<const T*>(u), u_stride, static_cast<T*>(state),
-          seq_start, seq_pos0, seq_len, seq_slot, n_seqs, C, taps);
-      B2_CHECK_LAUNCH("conv_state_update");
-    }
-  } else {
-    using T = float;
-    conv_headnorm_kvwrite_kernel<T><<<grid, CONV_WARPS * 32, 0, st>>>(static_cast<const T*>(u), u_stride, conv_w, static_cast<const T*>(state),
-        tok_seq, positions, seq_start, seq_pos0, seq_slot, slot_mapping, q_norm_w, k_norm_w, static_cast<T*>(q_out),
-        static_cast<T*>(k_cache), static_cast<T*>(v_cache), n_tokens, heads, kv_heads, dim, vdim, taps, eps);
-    B2_CHECK_LAUNCH("conv_headnorm_kvwrite");
-    if (taps > 1) {
-      conv_state_update_kernel<T><<<dim3((C + 127) / 128, n_seqs), 128, 0, st>>>(static_cast<const T*>(u), u_stride, static_cast<T*>(state),
-          seq_start, seq_pos0, seq_len, seq_slot, n_seqs, C, taps);
-      B2_CHECK_LAUNCH("conv_state_update");
-    }
-  }
+  // four channels per lane when every head slice and row starts on a 16-byte (float) / 8-byte (bf16) boundary
+  const bool vec4 = dim % 4 == 0 && vdim % 4 == 0 && u_stride % 4 == 0 && dim <= 128 * CONV4_CHUNKS && vdim <= 128 * CONV4_CHUNKS &&
+                    (taps == 1 || taps == 2 || taps == 3 || taps == 4) && aligned16(u) && aligned16(q_out) && aligned16(k_cache) &&
+                    aligned16(v_cache) && aligned16(conv_w) && aligned16(q_norm_w) && aligned16(k_norm_w) && (taps == 1 || aligned16(state));
+  if (dtype == B2TTS_DTYPE_BF16)
+    launch_conv<__nv_bfloat16>(vec4, grid, st, u, u_stride, conv_w, state, tok_seq, positions, seq_start, seq_pos0, seq_len, seq_slot,
+                               slot_mapping, q_norm_w, k_norm_w, q_out, k_cache, v_cache, n_tokens, n_seqs, heads, kv_heads, dim, vdim, taps, eps, C);
+  else
+    launch_conv<float>(vec4, grid, st, u, u_stride, conv_w, state, tok_seq, positions, seq_start, seq_pos0, seq_len, seq_slot,
+                       slot_mapping, q_norm_w, k_norm_w, q_out, k_cache, v_cache, n_tokens, n_seqs, heads, kv_heads, dim, vdim, taps, eps, C);
+  B2_CHECK_LAUNCH("conv_headnorm_kvwrite");
   return B2TTS_OK;
 }
 
@@ -456,5 +586,20 @@ extern "C" int b2tts_moe_route(const void* h, const float* router, int32_t* top_
   }
   moe_group_kernel<<<1, 1024, 0, st>>>(top_idx, offsets, sorted_pair, n_tokens * top, experts);
   B2_CHECK_LAUNCH("moe_group");
+  return B2TTS_OK;
+}
+
+extern "C" int b2tts_permute_rows(const void* in, void* out, const int32_t* idx, int rows, int cols, int div, int scatter, int dtype,
+                                  void* stream) {
+  using namespace b2;
+  B2_REQUIRE(rows >= 0 && cols > 0 && div > 0 && LM_DTYPE_OK(dtype), B2TTS_EINVAL, "permute_rows: bad arguments");
+  if (rows == 0) return B2TTS_OK;
+  B2_REQUIRE(in && out && idx, B2TTS_EINVAL, "permute_rows: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == B2TTS_DTYPE_BF16)
+    permute_rows_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), idx, cols, div, scatter);
+  else
+    permute_rows_kernel<float><<<rows, 256, 0, st>>>(static_cast<const float*>(in), static_cast<float*>(out), idx, cols, div, scatter);
+  B2_CHECK_LAUNCH("permute_rows");
   return B2TTS_OK;
 }

@@ -34,10 +34,11 @@ window_sigmoid_attn_kernel(const T* __restrict__ q /* [n, H*d] */, const T* __re
                            const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_pos0,
                            const int32_t* __restrict__ seq_len, const int32_t* __restrict__ block_tables, int bt_stride,
                            const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ pb,
-                           int H, int G, int d, int dv, int page, int window, float scale) {
+                           int H, int G, int d, int dv, int page, int window, float scale, int skip_single) {
   extern __shared__ __align__(16) float smem[];
   const int b = blockIdx.z, g = blockIdx.y;
   const int len = seq_len[b];
+  if (skip_single && len == 1) return;               // the streaming kernel below owns one-token rows
   const int rep = H / G;
   const int row0 = blockIdx.x * WA_ROWS;
   if (len <= 0) {
@@ -169,7 +170,7 @@ template <typename T, int DVL>
 static cudaError_t launch_window_attn(dim3 grid, size_t smem, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
                                       const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len,
                                       const int32_t* bt, int bt_stride, const float* r1, const float* r2, const float* pb, int H,
-                                      int G, int d, int dv, int page, int window, float scale) {
+                                      int G, int d, int dv, int page, int window, float scale, int skip_single) {
   auto kern = window_sigmoid_attn_kernel<T, DVL>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -177,8 +178,330 @@ static cudaError_t launch_window_attn(dim3 grid, size_t smem, cudaStream_t st, c
   }
   kern<<<grid, WA_WARPS * 32, smem, st>>>(static_cast<const T*>(q), static_cast<const T*>(kc), static_cast<const T*>(vc),
                                           static_cast<T*>(out), seq_start, seq_pos0, seq_len, bt, bt_stride, r1, r2, pb, H, G, d,
-                                          dv, page, window, scale);
+                                          dv, page, window, scale, skip_single);
   return cudaSuccess;
+}
+
+// ------------------------------------------------------------------ one new token per sequence: stream the window once
+// One CTA per (sequence, key/value head), 8 warps.  A key is read by LPK lanes, 16 bytes each, so a warp takes 32 / LPK
+// keys per load instruction and two such groups per iteration (all four loads are issued before the first use).  The
+// lane's slice of q stays in registers for every head of the group; a score is a dot over the slice plus log2(LPK)
+// shuffles; the weighted values accumulate per lane and are summed over key groups and warps at the end, in a fixed
+// order.  There is no split over keys: a window is a few hundred keys and the batch supplies the CTAs.
+constexpr int WD_WARPS = 8;
+constexpr int WD_UNROLL = 2;
+
+template <typename T> struct WdVec;
+template <> struct WdVec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void load(const __nv_bfloat16* p, float* f) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    f[0] = bf16lo(r.x); f[1] = bf16hi(r.x); f[2] = bf16lo(r.y); f[3] = bf16hi(r.y);
+    f[4] = bf16lo(r.z); f[5] = bf16hi(r.z); f[6] = bf16lo(r.w); f[7] = bf16hi(r.w);
+  }
+};
+template <> struct WdVec<float> {
+  static constexpr int N = 4;
+  __device__ static void load(const float* p, float* f) {
+    const float4 r = *reinterpret_cast<const float4*>(p);
+    f[0] = r.x; f[1] = r.y; f[2] = r.z; f[3] = r.w;
+  }
+};
+
+template <typename T, int LPK, int REP>
+__global__ void __launch_bounds__(WD_WARPS * 32)
+window_sigmoid_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                                  T* __restrict__ out, const int32_t* __restrict__ seq_start,
+                                  const int32_t* __restrict__ seq_pos0, const int32_t* __restrict__ seq_len,
+                                  const int32_t* __restrict__ block_tables, int bt_stride, const float* __restrict__ r1,
+                                  const float* __restrict__ r2, const float* __restrict__ pb, int H, int G, int d, int dv,
+                                  int page, int window, float scale) {
+  constexpr int VEC = WdVec<T>::N;
+  constexpr int KPI = 32 / LPK;                      // keys per warp load
+  extern __shared__ __align__(16) float red[];       // [WD_WARPS][rep][dv]
+  const int b = blockIdx.z, g = blockIdx.y;
+  const int len = seq_len[b];
+  const int rep = H / G;
+  const int n = seq_start[b];
+  if (len <= 0) {                                    // padding row of a captured step: defined output
+    for (int c = threadIdx.x; c < rep * dv; c += blockDim.x) out[static_cast<size_t>(n) * H * dv + g * rep * dv + c] = wa_from_f<T>(0.f);
+    return;
+  }
+  if (len != 1) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int grp = lane / LPK, c0 = (lane % LPK) * VEC;
+  const int p = seq_pos0[b];
+  const int j_lo = max(0, p - window + 1);
+  const int32_t* bt = block_tables + static_cast<size_t>(b) * bt_stride;
+  const bool has_k = c0 < d, has_v = c0 < dv;
+  float qv[REP][VEC], acc[REP][VEC], hr1[REP], hr2[REP], hpb[REP];
+#pragma unroll
+  for (int r = 0; r < REP; ++r) {
+    const bool ok = r < rep;
+    const int h = g * rep + (ok ? r : 0);
+    hr1[r] = r1[h]; hr2[r] = r2[h]; hpb[r] = pb[h];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) { qv[r][i] = 0.f; acc[r][i] = 0.f; }
+    if (ok && has_k) WdVec<T>::load(q + static_cast<size_t>(n) * H * d + h * d + c0, qv[r]);
+  }
+  for (int base = j_lo + warp * KPI * WD_UNROLL; base <= p; base += WD_WARPS * KPI * WD_UNROLL) {
+    float kf[WD_UNROLL][VEC], vf[WD_UNROLL][VEC];
+    int jj[WD_UNROLL];
+#pragma unroll
+    for (int u = 0; u < WD_UNROLL; ++u) {
+      const int j = base + u * KPI + grp;
+      jj[u] = j;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) { kf[u][i] = 0.f; vf[u][i] = 0.f; }
+      if (j <= p) {
+        const size_t slot = static_cast<size_t>(bt[j / page]) * page + j % page;
+        if (has_k) WdVec<T>::load(k_cache + slot * G * d + g * d + c0, kf[u]);
+        if (has_v) WdVec<T>::load(v_cache + slot * G * dv + g * dv + c0, vf[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < WD_UNROLL; ++u) {
+      const float dist = static_cast<float>(p - jj[u]);
+#pragma unroll
+      for (int r = 0; r < REP; ++r) {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) s = fmaf(qv[r][i], kf[u][i], s);
+#pragma unroll
+        for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        float w = 0.f;
+        if (jj[u] <= p && r < rep) {
+          const float z = s * scale - hr1[r] * log1pf(hr2[r] * dist) + hpb[r];
+          w = 1.0f / (1.0f + expf(-z));
+        }
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[r][i] = fmaf(w, vf[u][i], acc[r][i]);
+      }
+    }
+  }
+  // over the key groups of the warp, then over the warps
+#pragma unroll
+  for (int r = 0; r < REP; ++r)
+#pragma unroll
+    for (int i = 0; i < VEC; ++i)
+#pragma unroll
+      for (int o = LPK; o < 32; o <<= 1) acc[r][i] += __shfl_xor_sync(0xffffffffu, acc[r][i], o);
+  if (grp == 0 && has_v) {
+#pragma unroll
+    for (int r = 0; r < REP; ++r)
+      if (r < rep)
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) red[(warp * rep + r) * dv + c0 + i] = acc[r][i];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < rep * dv; idx += blockDim.x) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < WD_WARPS; ++w) t += red[w * rep * dv + idx];
+    out[static_cast<size_t>(n) * H * dv + g * rep * dv + idx] = wa_from_f<T>(t);
+  }
+}
+
+template <typename T, int LPK, int REP>
+static cudaError_t launch_window_decode(dim3 grid, size_t smem, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
+                                        const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* bt,
+                                        int bt_stride, const float* r1, const float* r2, const float* pb, int H, int G, int d, int dv,
+                                        int page, int window, float scale) {
+  auto kern = window_sigmoid_attn_decode_kernel<T, LPK, REP>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+  }
+  kern<<<grid, WD_WARPS * 32, smem, st>>>(static_cast<const T*>(q), static_cast<const T*>(kc), static_cast<const T*>(vc),
+                                          static_cast<T*>(out), seq_start, seq_pos0, seq_len, bt, bt_stride, r1, r2, pb, H, G, d, dv,
+                                          page, window, scale);
+  return cudaSuccess;
+}
+
+// ------------------------------------------------------------------ prompt portions on the tensor cores (bf16)
+// 64 query tokens of one head per CTA (4 warps x 16 rows), 64-key tiles gathered through the block table into padded
+// shared-memory rows.  S = Q K^T and O += P V run as m16n8k16 bf16 MMAs with float accumulators held in registers; the
+// weights are computed in float from the float scores, and enter the second product as a bf16 pair hi + lo
+// (lo = bf16(w - hi)), i.e. with 16 mantissa bits, so that no weight is rounded to bf16.  The distance bias of the
+// head, r1 * ln(1 + r2 * dist) - pb for dist < window, is tabulated once per CTA.
+__device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void split_bf16(float x, float y, uint32_t& hi, uint32_t& lo) {
+  const float xh = rbf(x), yh = rbf(y);
+  hi = pack_bf16(xh, yh);
+  lo = pack_bf16(x - xh, y - yh);
+}
+
+constexpr int WM_BM = 64, WM_BN = 64;
+
+template <int D, int DV>
+__global__ void __launch_bounds__(128)
+window_sigmoid_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                               const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
+                               const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_pos0,
+                               const int32_t* __restrict__ seq_len, const int32_t* __restrict__ block_tables, int bt_stride,
+                               const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ pb,
+                               int H, int G, int page, int window, float scale) {
+  constexpr int QS = D + 8, VS = DV + 8;             // padded rows: 16-byte aligned, ldmatrix rows land in distinct banks
+  extern __shared__ __align__(16) unsigned char wm_smem[];
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(wm_smem);
+  __nv_bfloat16* Ks = Qs + WM_BM * QS;
+  __nv_bfloat16* Vs = Ks + WM_BN * QS;
+  float* tab = reinterpret_cast<float*>(Vs + WM_BN * VS);
+  const int b = blockIdx.z, h = blockIdx.y, g = h / (H / G);
+  const int len = seq_len[b];
+  const int t0 = blockIdx.x * WM_BM;
+  if (len <= 1 || t0 >= len) return;                 // one-token and padding rows belong to the streaming kernel
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int start = seq_start[b], pos0 = seq_pos0[b];
+  const int32_t* bt = block_tables + static_cast<size_t>(b) * bt_stride;
+  for (int idx = tid; idx < WM_BM * (D / 8); idx += 128) {
+    const int r = idx / (D / 8), ch = idx % (D / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (t0 + r < len) v = ldg_v4(q + static_cast<size_t>(start + t0 + r) * H * D + h * D + ch * 8);
+    *reinterpret_cast<uint4*>(Qs + r * QS + ch * 8) = v;
+  }
+  {
+    const float a1 = r1[h], a2 = r2[h], a3 = pb[h];
+    for (int i = tid; i < window; i += 128) tab[i] = a1 * log1pf(a2 * static_cast<float>(i)) - a3;
+  }
+  const int t_hi = min(len - 1, t0 + WM_BM - 1);
+  const int j_lo = max(0, pos0 + t0 - window + 1), j_hi = pos0 + t_hi;
+  const int row_lo = warp * 16 + (lane >> 2);
+  const int p_lo = pos0 + t0 + row_lo, p_hi = p_lo + 8;
+  const bool ok_lo = t0 + row_lo < len, ok_hi = t0 + row_lo + 8 < len;
+  float oacc[DV / 8][4];
+#pragma unroll
+  for (int i = 0; i < DV / 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) oacc[i][e] = 0.f;
+
+  for (int j0 = j_lo; j0 <= j_hi; j0 += WM_BN) {
+    __syncthreads();
+    for (int idx = tid; idx < WM_BN * (D / 8); idx += 128) {
+      const int key = idx / (D / 8), ch = idx % (D / 8), j = j0 + key;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (j <= j_hi) v = ldg_v4(k_cache + (static_cast<size_t>(bt[j / page]) * page + j % page) * G * D + g * D + ch * 8);
+      *reinterpret_cast<uint4*>(Ks + key * QS + ch * 8) = v;
+    }
+    for (int idx = tid; idx < WM_BN * (DV / 8); idx += 128) {
+      const int key = idx / (DV / 8), ch = idx % (DV / 8), j = j0 + key;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (j <= j_hi) v = ldg_v4(v_cache + (static_cast<size_t>(bt[j / page]) * page + j % page) * G * DV + g * DV + ch * 8);
+      *reinterpret_cast<uint4*>(Vs + key * VS + ch * 8) = v;
+    }
+    __syncthreads();
+    // this warp's rows see keys p - window + 1 .. p: skip a tile none of its 16 rows can see
+    const int wp_lo = pos0 + t0 + warp * 16, wp_hi = wp_lo + 15;
+    if (j0 > wp_hi || j0 + WM_BN - 1 < wp_lo - window + 1 || t0 + warp * 16 >= len) continue;
+    float sacc[WM_BN / 8][4];
+#pragma unroll
+    for (int i = 0; i < WM_BN / 8; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sacc[i][e] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t a[4];
+      ldsm_x4(a[0], a[1], a[2], a[3], Qs + (warp * 16 + (lane & 15)) * QS + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int np = 0; np < WM_BN / 16; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4(b0, b1, b2, b3, Ks + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * QS + ks * 16 + ((lane >> 3) & 1) * 8);
+        mma_bf16_16816(sacc[2 * np], a, b0, b1);
+        mma_bf16_16816(sacc[2 * np + 1], a, b2, b3);
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < WM_BN / 8; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int j = j0 + nt * 8 + 2 * (lane & 3) + (e & 1);
+        const int dist = (e < 2 ? p_lo : p_hi) - j;
+        const bool ok = (e < 2 ? ok_lo : ok_hi) && dist >= 0 && dist < window;
+        float w = 0.f;
+        if (ok) w = __frcp_rn(1.0f + __expf(tab[dist] - sacc[nt][e] * scale));
+        sacc[nt][e] = w;
+      }
+    }
+#pragma unroll
+    for (int kk = 0; kk < WM_BN / 16; ++kk) {
+      uint32_t ah[4], al[4];
+      split_bf16(sacc[2 * kk][0], sacc[2 * kk][1], ah[0], al[0]);
+      split_bf16(sacc[2 * kk][2], sacc[2 * kk][3], ah[1], al[1]);
+      split_bf16(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1], ah[2], al[2]);
+      split_bf16(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3], ah[3], al[3]);
+#pragma unroll
+      for (int np = 0; np < DV / 16; ++np) {
+        uint32_t b0, b1, b2, b3;
+        ldsm_x4_t(b0, b1, b2, b3, Vs + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * VS + np * 16 + (lane >> 4) * 8);
+        mma_bf16_16816(oacc[2 * np], ah, b0, b1);
+        mma_bf16_16816(oacc[2 * np], al, b0, b1);
+        mma_bf16_16816(oacc[2 * np + 1], ah, b2, b3);
+        mma_bf16_16816(oacc[2 * np + 1], al, b2, b3);
+      }
+    }
+  }
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    if (!(half ? ok_hi : ok_lo)) continue;
+    __nv_bfloat16* o = out + static_cast<size_t>(start + t0 + row_lo + 8 * half) * H * DV + h * DV + 2 * (lane & 3);
+#pragma unroll
+    for (int nt = 0; nt < DV / 8; ++nt)
+      *reinterpret_cast<uint32_t*>(o + nt * 8) = pack_bf16(oacc[nt][2 * half], oacc[nt][2 * half + 1]);
+  }
+}
+
+template <int D>
+static cudaError_t launch_window_mma(dim3 grid, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
+                                     const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* bt,
+                                     int bt_stride, const float* r1, const float* r2, const float* pb, int H, int G, int page,
+                                     int window, float scale) {
+  auto kern = window_sigmoid_attn_mma_kernel<D, D>;
+  const size_t smem = sizeof(__nv_bfloat16) * (2 * WM_BM * (D + 8) + WM_BN * (D + 8)) + sizeof(float) * window;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  using B = __nv_bfloat16;
+  kern<<<grid, 128, smem, st>>>(static_cast<const B*>(q), static_cast<const B*>(kc), static_cast<const B*>(vc), static_cast<B*>(out),
+                                seq_start, seq_pos0, seq_len, bt, bt_stride, r1, r2, pb, H, G, page, window, scale);
+  return cudaSuccess;
+}
+
+template <typename T, int LPK>
+static cudaError_t launch_window_decode_rep(int rep, dim3 grid, size_t smem, cudaStream_t st, const void* q, const void* kc, const void* vc,
+                                            void* out, const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len,
+                                            const int32_t* bt, int bt_stride, const float* r1, const float* r2, const float* pb, int H,
+                                            int G, int d, int dv, int page, int window, float scale) {
+#define WD_GO(R) launch_window_decode<T, LPK, R>(grid, smem, st, q, kc, vc, out, seq_start, seq_pos0, seq_len, bt, bt_stride, r1, r2, pb, \
+                                                 H, G, d, dv, page, window, scale)
+  if (rep <= 1) return WD_GO(1);
+  if (rep <= 2) return WD_GO(2);
+  if (rep <= 4) return WD_GO(4);
+  return WD_GO(8);
+#undef WD_GO
+}
+
+template <typename T>
+static cudaError_t launch_window_decode_any(int lpk, int rep, dim3 grid, size_t smem, cudaStream_t st, const void* q, const void* kc,
+                                            const void* vc, void* out, const int32_t* seq_start, const int32_t* seq_pos0,
+                                            const int32_t* seq_len, const int32_t* bt, int bt_stride, const float* r1, const float* r2,
+                                            const float* pb, int H, int G, int d, int dv, int page, int window, float scale) {
+#define WD_GO(L) launch_window_decode_rep<T, L>(rep, grid, smem, st, q, kc, vc, out, seq_start, seq_pos0, seq_len, bt, bt_stride, r1, r2, \
+                                                pb, H, G, d, dv, page, window, scale)
+  if (lpk <= 8) return WD_GO(8);
+  if (lpk <= 16) return WD_GO(16);
+  return WD_GO(32);
+#undef WD_GO
 }
 
 }  // namespace b2
@@ -197,16 +520,47 @@ extern "C" int b2tts_window_sigmoid_attn(const void* q, const void* k_cache, con
   B2_REQUIRE(q && k_cache && v_cache && out && seq_start && seq_pos0 && seq_len && block_tables && r1 && r2 && pb, B2TTS_EINVAL,
              "window_sigmoid_attn: null pointer");
   const int rep = heads / kv_heads;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaSuccess;
+  // one-token rows: the streaming kernel, when the head sizes allow 16-byte slices and the group fits its registers
+  const int vec = dtype == B2TTS_DTYPE_BF16 ? 8 : 4;
+  const int widest = dim > vdim ? dim : vdim;
+  const bool stream_ok = dim % vec == 0 && vdim % vec == 0 && widest <= 32 * vec && rep <= 8 && aligned16(q) && aligned16(k_cache) &&
+                         aligned16(v_cache);
+  if (stream_ok) {
+    const int lpk = (widest + vec - 1) / vec;
+    const size_t smem_d = sizeof(float) * WD_WARPS * rep * vdim;
+    const dim3 grid_d(1, kv_heads, n_seqs);
+    if (dtype == B2TTS_DTYPE_BF16)
+      e = launch_window_decode_any<__nv_bfloat16>(lpk, rep, grid_d, smem_d, st, q, k_cache, v_cache, out, seq_start, seq_pos0, seq_len,
+                                                  block_tables, bt_stride, r1, r2, pb, heads, kv_heads, dim, vdim, page, window, scale);
+    else
+      e = launch_window_decode_any<float>(lpk, rep, grid_d, smem_d, st, q, k_cache, v_cache, out, seq_start, seq_pos0, seq_len,
+                                          block_tables, bt_stride, r1, r2, pb, heads, kv_heads, dim, vdim, page, window, scale);
+    if (e != cudaSuccess) return cuda_fail(e, "window_sigmoid_attn (streaming)");
+    B2_CHECK_LAUNCH("window_sigmoid_attn (streaming)");
+    if (max_new == 1) return B2TTS_OK;
+  }
+  // prompt portions in bf16 with a supported head size: the tensor-core kernel
+  if (stream_ok && dtype == B2TTS_DTYPE_BF16 && dim == vdim && (dim == 32 || dim == 64 || dim == 96 || dim == 128) && window <= 8192) {
+    const dim3 grid_m((max_new + WM_BM - 1) / WM_BM, heads, n_seqs);
+#define WM_GO(DD) e = launch_window_mma<DD>(grid_m, st, q, k_cache, v_cache, out, seq_start, seq_pos0, seq_len, block_tables, bt_stride, \
+                                            r1, r2, pb, heads, kv_heads, page, window, scale)
+    if (dim == 32) WM_GO(32); else if (dim == 64) WM_GO(64); else if (dim == 96) WM_GO(96); else WM_GO(128);
+#undef WM_GO
+    if (e != cudaSuccess) return cuda_fail(e, "window_sigmoid_attn (tensor)");
+    B2_CHECK_LAUNCH("window_sigmoid_attn (tensor)");
+    return B2TTS_OK;
+  }
+  const int skip_single = stream_ok ? 1 : 0;
   const int d4 = (dim + 3) & ~3;
   const size_t smem = sizeof(float) * (static_cast<size_t>(WA_ROWS) * d4 + WA_BK * (d4 + 4) + static_cast<size_t>(WA_BK) * vdim +
                                        WA_ROWS * (WA_BK + 1));
   B2_REQUIRE(smem <= 200 * 1024, B2TTS_EUNSUPPORTED, "window_sigmoid_attn: head size %d needs %zu bytes of shared memory", dim, smem);
   const dim3 grid((static_cast<unsigned>(max_new) * rep + WA_ROWS - 1) / WA_ROWS, kv_heads, n_seqs);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int dvl = (vdim + 31) / 32;
-  cudaError_t e;
 #define WA_GO(T, L) e = launch_window_attn<T, L>(grid, smem, st, q, k_cache, v_cache, out, seq_start, seq_pos0, seq_len, block_tables, \
-                                                 bt_stride, r1, r2, pb, heads, kv_heads, dim, vdim, page, window, scale)
+                                                 bt_stride, r1, r2, pb, heads, kv_heads, dim, vdim, page, window, scale, skip_single)
   if (dtype == B2TTS_DTYPE_BF16) {
     if (dvl <= 1) WA_GO(__nv_bfloat16, 1); else if (dvl <= 2) WA_GO(__nv_bfloat16, 2); else if (dvl <= 4) WA_GO(__nv_bfloat16, 4); else WA_GO(__nv_bfloat16, 8);
   } else {

@@ -92,7 +92,7 @@ def test_embed_residual_and_gain_norm(nat, dtype, cols):
 
 
 @pytest.mark.parametrize("taps", [1, 2, 4, 5])
-@pytest.mark.parametrize("H,G,d,dv", [(4, 2, 24, 40), (3, 3, 32, 8), (6, 1, 64, 64)])
+@pytest.mark.parametrize("H,G,d,dv", [(4, 2, 24, 40), (3, 3, 32, 8), (8, 1, 64, 64)])
 def test_short_conv_head_norm_cache_write_in_portions(nat, taps, H, G, d, dv):
     """The convolution over a sequence cut into portions (1, 2, 3, 7 ... tokens) with its carried state, in a state
     slot that another sequence used before, beside a second sequence; k and v land in scattered pages."""
@@ -170,7 +170,7 @@ def _attn_case(nat, H, G, d, dv, window, page, seqs, dtype=torch.float32, spike=
     return out, torch.cat(refs)
 
 
-@pytest.mark.parametrize("H,G,d,dv", [(6, 1, 64, 64), (4, 2, 24, 40), (3, 3, 130, 200), (8, 2, 16, 12)])
+@pytest.mark.parametrize("H,G,d,dv", [(8, 1, 64, 64), (4, 2, 24, 40), (3, 3, 130, 200), (8, 2, 16, 12)])
 @pytest.mark.parametrize("window", [1, 5, 33, 100])
 def test_window_sigmoid_attention_mixed_batch(nat, H, G, d, dv, window):
     out, ref = _attn_case(nat, H, G, d, dv, window, 16, [(0, 50), (37, 1), (20, 23), (63, 2), (0, 1)], seed=window)
@@ -198,7 +198,57 @@ def test_window_edge_key_dominates(nat, window, page, decode):
             assert (out[row].abs().max().item() > 500) == seen
 
 
-@pytest.mark.parametrize("E,top,cols", [(5, 2, 48), (16, 3, 256), (4, 4, 40), (7, 1, 100), (70, 6, 64)])
+@pytest.mark.parametrize("H,G,d", [(8, 1, 64), (4, 2, 32), (4, 4, 128), (3, 1, 96)])
+@pytest.mark.parametrize("window", [1, 33, 64, 65, 200, 1000])
+def test_bfloat16_prompt_portions_on_the_tensor_cores(nat, H, G, d, window):
+    """Prompt portions longer than one query tile and one key tile, after cached tokens, beside single tokens, in
+    16-token pages: bfloat16 inputs against the plain model on the same (rounded) inputs."""
+    out, ref = _attn_case(nat, H, G, d, d, window, 16, [(0, 150), (100, 90), (37, 1), (3, 67), (0, 1), (129, 2)],
+                          dtype=torch.bfloat16, seed=window)
+    assert rel(out, ref) < 1e-2
+
+
+@pytest.mark.parametrize("window,page", [(17, 16), (64, 64), (70, 64), (129, 16)])
+def test_bfloat16_window_edge_key_dominates(nat, window, page):
+    T = 300
+    for j in (0, page - 1, 64, 2 * page + 3):
+        for i in (j + window - 1, j + window):
+            for decode in (False, True):
+                cached, new = (i, 1) if decode else (max(0, i - 70), min(T, i + 3) - max(0, i - 70))
+                out, ref = _attn_case(nat, 4, 2, 32, 32, window, page, [(cached, new)], dtype=torch.bfloat16, spike=(0, j), seed=j)
+                row = i - cached
+                seen = ref[row].abs().max().item() > 500
+                assert seen == (i - j < window)
+                assert (out[row].float().abs().max().item() > 500) == seen
+                assert rel(out, ref) < 1e-2
+
+
+def test_experts_as_sorted_gemms_equal_the_grouped_launch(nat):
+    """Above its pair threshold the mixture gathers rows by expert and runs one GEMM pair per expert; same result as
+    the grouped launch and as the plain model, also with an expert nobody chose."""
+    from nano_qwen3tts_vllm_b200.layers.moe import SigmoidTopKMoE
+    g = torch.Generator().manual_seed(11)
+    E, top, cols, ff, n = 6, 2, 64, 40, 300
+    for dtype, tol in ((torch.float32, 2e-5), (torch.bfloat16, 3e-2)):
+        moe = SigmoidTopKMoE(cols, ff, E, top, 0.8).to(DEV)
+        router = torch.randn(E, cols, generator=g) * 0.3
+        router[4] = -10.0 * torch.ones(cols)                       # h > 0 below: expert 4 is never chosen
+        up = (torch.randn(E, ff, cols, generator=g) * cols ** -0.5).to(dtype)
+        down = (torch.randn(E, cols, ff, generator=g) * ff ** -0.5).to(dtype)
+        h = (torch.rand(n, cols, generator=g) + 0.1).to(dtype)
+        moe.router.copy_(router)
+        moe.up.data, moe.down.data = up.to(DEV), down.to(DEV)
+        ref = O.moe_ff(h.double(), router.double(), list(up.double()), list(down.double()), top, 0.8)
+        outs = []
+        for thr in (1, 10 ** 9):
+            moe.SORTED_GEMM_MIN_PAIRS = thr
+            z, zw = moe(h.to(DEV))
+            outs.append((zw.double().cpu()[:, :, None] * z.double().cpu().view(n, top, cols)).sum(1))
+            assert rel(outs[-1], ref) < tol
+        assert rel(outs[0], outs[1]) < tol
+
+
+@pytest.mark.parametrize("E,top,cols", [(5, 2, 48), (12, 3, 256), (4, 4, 40), (7, 1, 100), (70, 6, 64)])
 def test_router_and_grouped_experts(nat, E, top, cols):
     from nano_qwen3tts_vllm_b200.layers.moe import SigmoidTopKMoE
     g = torch.Generator().manual_seed(E)
