@@ -223,7 +223,11 @@ template <> struct Vec4<__nv_bfloat16> {
   __device__ static void store(__nv_bfloat16* p, const float* f) { *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3])); }
 };
 constexpr int CONV4_CHUNKS = 2;            // head sizes up to 256
+constexpr int CONV4_TOKENS = 8;            // consecutive rows of the step per warp: the taps' weights are loaded once for all
 
+// One warp per (block of CONV4_TOKENS rows, head slice).  The lane keeps the taps of its four channels in registers and
+// walks the rows; a row's earlier taps were the previous rows' loads (same addresses: they hit in L1), so u is read
+// from memory about once.
 template <typename T, int TAPS>
 __global__ void __launch_bounds__(CONV_WARPS * 32)
 conv_headnorm_kvwrite_vec4_kernel(const T* __restrict__ u, int64_t u_stride, const float* __restrict__ conv_w,
@@ -236,83 +240,90 @@ conv_headnorm_kvwrite_vec4_kernel(const T* __restrict__ u, int64_t u_stride, con
   const int lane = threadIdx.x & 31;
   const int item = blockIdx.x * CONV_WARPS + (threadIdx.x >> 5);
   const int heads = H + 2 * G;
-  if (item >= n_tokens * heads) return;
-  const int n = item / heads, hs = item % heads;
-  const int slot = slot_mapping[n];
-  if (slot < 0) return;
+  const int n_blocks = (n_tokens + CONV4_TOKENS - 1) / CONV4_TOKENS;
+  if (item >= n_blocks * heads) return;
+  const int n0 = (item / heads) * CONV4_TOKENS, hs = item % heads;
   const int C = H * d + G * d + G * dv;
   int kind, head, width, c0;
   if (hs < H) { kind = 0; head = hs; width = d; c0 = head * d; }
   else if (hs < H + G) { kind = 1; head = hs - H; width = d; c0 = H * d + head * d; }
   else { kind = 2; head = hs - H - G; width = dv; c0 = H * d + G * d + head * dv; }
-  const int b = tok_seq[n], p = positions[n];
-  const int pos0 = seq_pos0[b], start = seq_start[b], sslot = seq_slot[b];
   constexpr int R = TAPS - 1;
-  const T* src[TAPS];                      // row of tap j (nullptr: before the sequence's start)
-#pragma unroll
-  for (int j = 0; j < TAPS; ++j) {
-    const int pj = p - R + j;
-    src[j] = nullptr;
-    if (pj >= pos0) src[j] = u + static_cast<int64_t>(start + pj - pos0) * u_stride;
-    else if (pj >= 0) src[j] = state + (static_cast<size_t>(sslot) * R + (pj - (pos0 - R))) * C;
-  }
-  float y[CONV4_CHUNKS][4];
-  float ssq = 0.f;
+  float w[CONV4_CHUNKS][4][TAPS];
+  float g4[CONV4_CHUNKS][4];
 #pragma unroll
   for (int i = 0; i < CONV4_CHUNKS; ++i) {
     const int cc = (lane + 32 * i) * 4;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) y[i][e] = 0.f;
+    for (int e = 0; e < 4; ++e) {
+      g4[i][e] = 0.f;
+#pragma unroll
+      for (int j = 0; j < TAPS; ++j) w[i][e][j] = 0.f;
+    }
     if (cc < width) {
-      const int c = c0 + cc;
-      float w[4][TAPS];
-      if constexpr (TAPS == 4) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float4 r = *reinterpret_cast<const float4*>(conv_w + static_cast<size_t>(c + e) * TAPS);
-          w[e][0] = r.x; w[e][1] = r.y; w[e][2] = r.z; w[e][3] = r.w;
-        }
-      } else {
+      for (int e = 0; e < 4; ++e)
 #pragma unroll
-        for (int e = 0; e < 4; ++e)
-#pragma unroll
-          for (int j = 0; j < TAPS; ++j) w[e][j] = conv_w[static_cast<size_t>(c + e) * TAPS + j];
-      }
-#pragma unroll
-      for (int j = 0; j < TAPS; ++j) {
-        if (src[j] != nullptr) {
-          float uv[4];
-          Vec4<T>::load(src[j] + c, uv);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) y[i][e] = fmaf(w[e][j], uv[e], y[i][e]);
-        }
+        for (int j = 0; j < TAPS; ++j) w[i][e][j] = conv_w[static_cast<size_t>(c0 + cc + e) * TAPS + j];
+      if (kind != 2) {
+        const float4 r = *reinterpret_cast<const float4*>((kind == 0 ? q_norm_w : k_norm_w) + cc);
+        g4[i][0] = r.x; g4[i][1] = r.y; g4[i][2] = r.z; g4[i][3] = r.w;
       }
     }
   }
-  if (kind != 2) {
+  const int n_end = min(n_tokens, n0 + CONV4_TOKENS);
+  for (int n = n0; n < n_end; ++n) {
+    const int slot = slot_mapping[n];
+    if (slot < 0) continue;                  // padding row
+    const int b = tok_seq[n], p = positions[n];
+    const int pos0 = seq_pos0[b], start = seq_start[b], sslot = seq_slot[b];
+    const T* src[TAPS];                      // row of tap j (nullptr: before the sequence's start)
 #pragma unroll
-    for (int i = 0; i < CONV4_CHUNKS; ++i)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) { y[i][e] = to_f(from_f<T>(y[i][e])); ssq += y[i][e] * y[i][e]; }
-    ssq = warp_sum(ssq);
-    const float inv = 1.0f / sqrtf(ssq / static_cast<float>(width) + eps);
-    const float* nw = kind == 0 ? q_norm_w : k_norm_w;
+    for (int j = 0; j < TAPS; ++j) {
+      const int pj = p - R + j;
+      src[j] = nullptr;
+      if (pj >= pos0) src[j] = u + static_cast<int64_t>(start + pj - pos0) * u_stride;
+      else if (pj >= 0) src[j] = state + (static_cast<size_t>(sslot) * R + (pj - (pos0 - R))) * C;
+    }
+    float y[CONV4_CHUNKS][4];
 #pragma unroll
     for (int i = 0; i < CONV4_CHUNKS; ++i) {
       const int cc = (lane + 32 * i) * 4;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) y[i][e] = 0.f;
       if (cc < width) {
-        const float4 g4 = *reinterpret_cast<const float4*>(nw + cc);
-        y[i][0] *= inv * g4.x; y[i][1] *= inv * g4.y; y[i][2] *= inv * g4.z; y[i][3] *= inv * g4.w;
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) {
+          if (src[j] != nullptr) {
+            float uv[4];
+            Vec4<T>::load(src[j] + c0 + cc, uv);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) y[i][e] = fmaf(w[i][e][j], uv[e], y[i][e]);
+          }
+        }
       }
     }
-  }
-  T* dst = kind == 0 ? q_out + static_cast<size_t>(n) * H * d + head * d
-         : kind == 1 ? k_cache + static_cast<size_t>(slot) * G * d + head * d
-                     : v_cache + static_cast<size_t>(slot) * G * dv + head * dv;
+    if (kind != 2) {
+      float ssq = 0.f;
 #pragma unroll
-  for (int i = 0; i < CONV4_CHUNKS; ++i) {
-    const int cc = (lane + 32 * i) * 4;
-    if (cc < width) Vec4<T>::store(dst + cc, y[i]);
+      for (int i = 0; i < CONV4_CHUNKS; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { y[i][e] = to_f(from_f<T>(y[i][e])); ssq += y[i][e] * y[i][e]; }
+      ssq = warp_sum(ssq);
+      const float inv = 1.0f / sqrtf(ssq / static_cast<float>(width) + eps);
+#pragma unroll
+      for (int i = 0; i < CONV4_CHUNKS; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) y[i][e] *= inv * g4[i][e];
+    }
+    T* dst = kind == 0 ? q_out + static_cast<size_t>(n) * H * d + head * d
+           : kind == 1 ? k_cache + static_cast<size_t>(slot) * G * d + head * d
+                       : v_cache + static_cast<size_t>(slot) * G * dv + head * dv;
+#pragma unroll
+    for (int i = 0; i < CONV4_CHUNKS; ++i) {
+      const int cc = (lane + 32 * i) * 4;
+      if (cc < width) Vec4<T>::store(dst + cc, y[i]);
+    }
   }
 }
 
@@ -440,6 +451,7 @@ static void launch_conv(bool vec4, int grid, cudaStream_t st, const void* u, int
 #define CONV4_GO(TP) conv_headnorm_kvwrite_vec4_kernel<T, TP><<<grid, CONV_WARPS * 32, 0, st>>>(static_cast<const T*>(u), u_stride, conv_w, \
       static_cast<const T*>(state), tok_seq, positions, seq_start, seq_pos0, seq_slot, slot_mapping, q_norm_w, k_norm_w, \
       static_cast<T*>(q_out), static_cast<T*>(k_cache), static_cast<T*>(v_cache), n_tokens, H, G, d, dv, eps)
+  if (vec4) grid = ((n_tokens + CONV4_TOKENS - 1) / CONV4_TOKENS * (H + 2 * G) + CONV_WARPS - 1) / CONV_WARPS;
   if (vec4 && taps == 4) CONV4_GO(4);
   else if (vec4 && taps == 3) CONV4_GO(3);
   else if (vec4 && taps == 2) CONV4_GO(2);

@@ -184,29 +184,31 @@ static cudaError_t launch_window_attn(dim3 grid, size_t smem, cudaStream_t st, c
 
 // ------------------------------------------------------------------ one new token per sequence: stream the window once
 // One CTA per (sequence, key/value head), 8 warps.  A key is read by LPK lanes, 16 bytes each, so a warp takes 32 / LPK
-// keys per load instruction and two such groups per iteration (all four loads are issued before the first use).  The
+// keys per load instruction and four such groups per iteration: all eight loads are issued, as raw 16-byte registers,
+// before the first use, and the pages of the window are looked up once per CTA into shared memory.  The
 // lane's slice of q stays in registers for every head of the group; a score is a dot over the slice plus log2(LPK)
 // shuffles; the weighted values accumulate per lane and are summed over key groups and warps at the end, in a fixed
 // order.  There is no split over keys: a window is a few hundred keys and the batch supplies the CTAs.
 constexpr int WD_WARPS = 8;
-constexpr int WD_UNROLL = 2;
+constexpr int WD_UNROLL = 4;
 
 template <typename T> struct WdVec;
 template <> struct WdVec<__nv_bfloat16> {
   static constexpr int N = 8;
-  __device__ static void load(const __nv_bfloat16* p, float* f) {
-    const uint4 r = *reinterpret_cast<const uint4*>(p);
+  __device__ static void cvt(const uint4& r, float* f) {
     f[0] = bf16lo(r.x); f[1] = bf16hi(r.x); f[2] = bf16lo(r.y); f[3] = bf16hi(r.y);
     f[4] = bf16lo(r.z); f[5] = bf16hi(r.z); f[6] = bf16lo(r.w); f[7] = bf16hi(r.w);
   }
 };
 template <> struct WdVec<float> {
   static constexpr int N = 4;
-  __device__ static void load(const float* p, float* f) {
-    const float4 r = *reinterpret_cast<const float4*>(p);
-    f[0] = r.x; f[1] = r.y; f[2] = r.z; f[3] = r.w;
+  __device__ static void cvt(const uint4& r, float* f) {
+    f[0] = __uint_as_float(r.x); f[1] = __uint_as_float(r.y); f[2] = __uint_as_float(r.z); f[3] = __uint_as_float(r.w);
   }
 };
+template <typename T> __device__ __forceinline__ void wd_load(const T* p, float* f) {
+  WdVec<T>::cvt(*reinterpret_cast<const uint4*>(p), f);
+}
 
 template <typename T, int LPK, int REP>
 __global__ void __launch_bounds__(WD_WARPS * 32)
@@ -242,40 +244,48 @@ window_sigmoid_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__
     hr1[r] = r1[h]; hr2[r] = r2[h]; hpb[r] = pb[h];
 #pragma unroll
     for (int i = 0; i < VEC; ++i) { qv[r][i] = 0.f; acc[r][i] = 0.f; }
-    if (ok && has_k) WdVec<T>::load(q + static_cast<size_t>(n) * H * d + h * d + c0, qv[r]);
+    if (ok && has_k) wd_load(q + static_cast<size_t>(n) * H * d + h * d + c0, qv[r]);
   }
+  // the window's pages, once: pages[i] = block table entry of page pg0 + i
+  int32_t* pages = reinterpret_cast<int32_t*>(red + WD_WARPS * rep * dv);
+  const int pg0 = j_lo / page;
+  for (int i = threadIdx.x; i <= p / page - pg0; i += blockDim.x) pages[i] = bt[pg0 + i];
+  __syncthreads();
   for (int base = j_lo + warp * KPI * WD_UNROLL; base <= p; base += WD_WARPS * KPI * WD_UNROLL) {
-    float kf[WD_UNROLL][VEC], vf[WD_UNROLL][VEC];
-    int jj[WD_UNROLL];
+    uint4 kr[WD_UNROLL], vr[WD_UNROLL];
 #pragma unroll
     for (int u = 0; u < WD_UNROLL; ++u) {
       const int j = base + u * KPI + grp;
-      jj[u] = j;
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) { kf[u][i] = 0.f; vf[u][i] = 0.f; }
+      kr[u] = make_uint4(0, 0, 0, 0);
+      vr[u] = make_uint4(0, 0, 0, 0);
       if (j <= p) {
-        const size_t slot = static_cast<size_t>(bt[j / page]) * page + j % page;
-        if (has_k) WdVec<T>::load(k_cache + slot * G * d + g * d + c0, kf[u]);
-        if (has_v) WdVec<T>::load(v_cache + slot * G * dv + g * dv + c0, vf[u]);
+        const int pg = j / page;
+        const size_t slot = static_cast<size_t>(pages[pg - pg0]) * page + (j - pg * page);
+        if (has_k) kr[u] = ldg_v4(k_cache + slot * G * d + g * d + c0);
+        if (has_v) vr[u] = ldg_v4(v_cache + slot * G * dv + g * dv + c0);
       }
     }
 #pragma unroll
     for (int u = 0; u < WD_UNROLL; ++u) {
-      const float dist = static_cast<float>(p - jj[u]);
+      const int j = base + u * KPI + grp;
+      const float dist = static_cast<float>(p - j);
+      float kf[VEC], vf[VEC];
+      WdVec<T>::cvt(kr[u], kf);
+      WdVec<T>::cvt(vr[u], vf);
 #pragma unroll
       for (int r = 0; r < REP; ++r) {
         float s = 0.f;
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) s = fmaf(qv[r][i], kf[u][i], s);
+        for (int i = 0; i < VEC; ++i) s = fmaf(qv[r][i], kf[i], s);
 #pragma unroll
         for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         float w = 0.f;
-        if (jj[u] <= p && r < rep) {
+        if (j <= p && r < rep) {
           const float z = s * scale - hr1[r] * log1pf(hr2[r] * dist) + hpb[r];
           w = 1.0f / (1.0f + expf(-z));
         }
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) acc[r][i] = fmaf(w, vf[u][i], acc[r][i]);
+        for (int i = 0; i < VEC; ++i) acc[r][i] = fmaf(w, vf[i], acc[r][i]);
       }
     }
   }
@@ -529,7 +539,7 @@ extern "C" int b2tts_window_sigmoid_attn(const void* q, const void* k_cache, con
                          aligned16(v_cache);
   if (stream_ok) {
     const int lpk = (widest + vec - 1) / vec;
-    const size_t smem_d = sizeof(float) * WD_WARPS * rep * vdim;
+    const size_t smem_d = sizeof(float) * WD_WARPS * rep * vdim + sizeof(int32_t) * ((window + page - 1) / page + 2);
     const dim3 grid_d(1, kv_heads, n_seqs);
     if (dtype == B2TTS_DTYPE_BF16)
       e = launch_window_decode_any<__nv_bfloat16>(lpk, rep, grid_d, smem_d, st, q, k_cache, v_cache, out, seq_start, seq_pos0, seq_len,
