@@ -464,9 +464,6 @@ B2TTS_API int b2tts_moe_route(const void* h, const float* router, int32_t* top_i
 B2TTS_API int b2tts_grouped_gemm(const void* a, int64_t lda, const void* w, void* c, int64_t ldc, const int32_t* offsets,
                                  const int32_t* sorted_pair, int n_pairs, int experts, int n, int k, int top, int in_by_token,
                                  int out_by_pair, int act, int dtype, void* stream);
-/* Rows moved by an index list: gather out[i] = in[idx[i] / div], or (scatter != 0) out[idx[i]] = in[i]. */
-B2TTS_API int b2tts_permute_rows(const void* in, void* out, const int32_t* idx, int rows, int cols, int div, int scatter, int dtype,
-                                 void* stream);
 
 #ifdef __cplusplus
 }

@@ -87,7 +87,6 @@ def _load():
         "b2tts_window_sigmoid_attn": (I, [P, P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P]),
         "b2tts_moe_route": (I, [P, P, P, P, P, P, I, I, I, I, F, I, P]),
         "b2tts_grouped_gemm": (I, [P, L, P, P, L, P, P, I, I, I, I, I, I, I, I, I, P]),
-        "b2tts_permute_rows": (I, [P, P, P, I, I, I, I, I, P]),
     }
     for name, (res, args) in sig.items():
         if not hasattr(lib, name):
@@ -771,13 +770,3 @@ def grouped_gemm(a, w, c, offsets, sorted_pair, n_pairs, top, in_by_token, out_b
     _check(_load().b2tts_grouped_gemm(a.data_ptr(), a.stride(0), w.data_ptr(), c.data_ptr(), c.stride(0), offsets.data_ptr(),
                                       sorted_pair.data_ptr(), n_pairs, e, n, k, top, int(in_by_token), int(out_by_pair), int(act),
                                       dt, _stream()), "grouped_gemm")
-
-
-def permute_rows(src, out, idx, div=1, scatter=False):
-    """gather: out[i] = src[idx[i] // div]; scatter: out[idx[i]] = src[i]."""
-    dt = _act(src, "src")
-    assert out.dtype == src.dtype and out.is_contiguous() and src.shape[1] == out.shape[1]
-    _cuda(idx, I32, "idx")
-    _check(_load().b2tts_permute_rows(src.data_ptr(), out.data_ptr(), idx.data_ptr(), idx.shape[0], src.shape[1], div, int(scatter), dt,
-                                      _stream()), "permute_rows")
-    return out

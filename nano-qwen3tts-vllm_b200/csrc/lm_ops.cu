@@ -271,12 +271,23 @@ conv_headnorm_kvwrite_vec4_kernel(const T* __restrict__ u, int64_t u_stride, con
       }
     }
   }
-  const int n_end = min(n_tokens, n0 + CONV4_TOKENS);
-  for (int n = n0; n < n_end; ++n) {
-    const int slot = slot_mapping[n];
-    if (slot < 0) continue;                  // padding row
-    const int b = tok_seq[n], p = positions[n];
-    const int pos0 = seq_pos0[b], start = seq_start[b], sslot = seq_slot[b];
+  // the rows' bookkeeping (three dependent loads each) is fetched by one lane per row, all rows at once
+  int m_slot = -1, m_p = 0, m_pos0 = 0, m_start = 0, m_sslot = 0;
+  if (lane < CONV4_TOKENS && n0 + lane < n_tokens) {
+    m_slot = slot_mapping[n0 + lane];
+    if (m_slot >= 0) {
+      const int b = tok_seq[n0 + lane];
+      m_p = positions[n0 + lane];
+      m_pos0 = seq_pos0[b]; m_start = seq_start[b]; m_sslot = seq_slot[b];
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < CONV4_TOKENS; ++t) {
+    const int n = n0 + t;
+    const int slot = __shfl_sync(0xffffffffu, m_slot, t);
+    if (slot < 0) continue;                  // padding row, or past the step's last row
+    const int p = __shfl_sync(0xffffffffu, m_p, t), pos0 = __shfl_sync(0xffffffffu, m_pos0, t);
+    const int start = __shfl_sync(0xffffffffu, m_start, t), sslot = __shfl_sync(0xffffffffu, m_sslot, t);
     const T* src[TAPS];                      // row of tap j (nullptr: before the sequence's start)
 #pragma unroll
     for (int j = 0; j < TAPS; ++j) {
@@ -355,18 +366,6 @@ __global__ void conv_state_update_kernel(const T* __restrict__ u, int64_t u_stri
       st[static_cast<size_t>(r) * C] = v;
     }
   }
-}
-
-// ------------------------------------------------------------------ row gather / scatter by an index list
-// gather:  out[i] = in[idx[i] / div]      scatter:  out[idx[i]] = in[i]        (rows of `cols` elements)
-template <typename T>
-__global__ void permute_rows_kernel(const T* __restrict__ in, T* __restrict__ out, const int32_t* __restrict__ idx, int cols, int div,
-                                    int scatter) {
-  const size_t i = blockIdx.x;
-  const size_t j = static_cast<size_t>(idx[i]) / div;
-  const T* src = in + (scatter ? i : j) * cols;
-  T* dst = out + (scatter ? j : i) * cols;
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) dst[c] = src[c];
 }
 
 // ------------------------------------------------------------------ sigmoid top-k router
@@ -598,20 +597,5 @@ extern "C" int b2tts_moe_route(const void* h, const float* router, int32_t* top_
   }
   moe_group_kernel<<<1, 1024, 0, st>>>(top_idx, offsets, sorted_pair, n_tokens * top, experts);
   B2_CHECK_LAUNCH("moe_group");
-  return B2TTS_OK;
-}
-
-extern "C" int b2tts_permute_rows(const void* in, void* out, const int32_t* idx, int rows, int cols, int div, int scatter, int dtype,
-                                  void* stream) {
-  using namespace b2;
-  B2_REQUIRE(rows >= 0 && cols > 0 && div > 0 && LM_DTYPE_OK(dtype), B2TTS_EINVAL, "permute_rows: bad arguments");
-  if (rows == 0) return B2TTS_OK;
-  B2_REQUIRE(in && out && idx, B2TTS_EINVAL, "permute_rows: null pointer");
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == B2TTS_DTYPE_BF16)
-    permute_rows_kernel<__nv_bfloat16><<<rows, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), idx, cols, div, scatter);
-  else
-    permute_rows_kernel<float><<<rows, 256, 0, st>>>(static_cast<const float*>(in), static_cast<float*>(out), idx, cols, div, scatter);
-  B2_CHECK_LAUNCH("permute_rows");
   return B2TTS_OK;
 }

@@ -334,19 +334,6 @@ static cudaError_t launch_window_decode(dim3 grid, size_t smem, cudaStream_t st,
 // weights are computed in float from the float scores, and enter the second product as a bf16 pair hi + lo
 // (lo = bf16(w - hi)), i.e. with 16 mantissa bits, so that no weight is rounded to bf16.  The distance bias of the
 // head, r1 * ln(1 + r2 * dist) - pb for dist < window, is tabulated once per CTA.
-__device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_u32(p)));
-}
-__device__ __forceinline__ void ldsm_x4_t(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(smem_u32(p)));
-}
-__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
 __device__ __forceinline__ void split_bf16(float x, float y, uint32_t& hi, uint32_t& lo) {
   const float xh = rbf(x), yh = rbf(y);
   hi = pack_bf16(xh, yh);
@@ -355,66 +342,86 @@ __device__ __forceinline__ void split_bf16(float x, float y, uint32_t& hi, uint3
 
 constexpr int WM_BM = 64, WM_BN = 64;
 
-template <int D, int DV>
-__global__ void __launch_bounds__(128)
+// REPB query heads of one key/value group share the CTA (4 warps each) and with it every K/V tile; the tiles arrive by
+// 16-byte asynchronous copies into a two-stage ring, so tile t + 1 is in flight while tile t is multiplied.
+template <int D, int DV, int REPB>
+__global__ void __launch_bounds__(128 * REPB, 4 / REPB)
 window_sigmoid_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                                const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
                                const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_pos0,
                                const int32_t* __restrict__ seq_len, const int32_t* __restrict__ block_tables, int bt_stride,
                                const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ pb,
-                               int H, int G, int page, int window, float scale) {
+                               int H, int G, int page, int page_shift, int window, float scale) {
+  static_assert(D == DV, "one slot computation serves the K and the V chunk");
   constexpr int QS = D + 8, VS = DV + 8;             // padded rows: 16-byte aligned, ldmatrix rows land in distinct banks
+  constexpr int NT = 128 * REPB;
+  constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ __align__(16) unsigned char wm_smem[];
-  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(wm_smem);
-  __nv_bfloat16* Ks = Qs + WM_BM * QS;
-  __nv_bfloat16* Vs = Ks + WM_BN * QS;
-  float* tab = reinterpret_cast<float*>(Vs + WM_BN * VS);
-  const int b = blockIdx.z, h = blockIdx.y, g = h / (H / G);
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(wm_smem);       // [REPB][BM][QS]
+  __nv_bfloat16* Ks = Qs + REPB * WM_BM * QS;                          // [2][BN][QS]
+  __nv_bfloat16* Vs = Ks + 2 * WM_BN * QS;                             // [2][BN][VS]
+  float* tab = reinterpret_cast<float*>(Vs + 2 * WM_BN * VS);          // [REPB][window]
+  const int b = blockIdx.z, h0 = blockIdx.y * REPB, g = h0 / (H / G);
   const int len = seq_len[b];
   const int t0 = blockIdx.x * WM_BM;
   if (len <= 1 || t0 >= len) return;                 // one-token and padding rows belong to the streaming kernel
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int hw = warp >> 2, wr = warp & 3;           // this warp: head h0 + hw, rows wr * 16 ..
   const int start = seq_start[b], pos0 = seq_pos0[b];
   const int32_t* bt = block_tables + static_cast<size_t>(b) * bt_stride;
-  for (int idx = tid; idx < WM_BM * (D / 8); idx += 128) {
-    const int r = idx / (D / 8), ch = idx % (D / 8);
+  for (int idx = tid; idx < REPB * WM_BM * (D / 8); idx += NT) {
+    const int hr = idx / (WM_BM * (D / 8)), r = idx / (D / 8) % WM_BM, ch = idx % (D / 8);
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (t0 + r < len) v = ldg_v4(q + static_cast<size_t>(start + t0 + r) * H * D + h * D + ch * 8);
-    *reinterpret_cast<uint4*>(Qs + r * QS + ch * 8) = v;
+    if (t0 + r < len) v = ldg_v4(q + static_cast<size_t>(start + t0 + r) * H * D + (h0 + hr) * D + ch * 8);
+    *reinterpret_cast<uint4*>(Qs + (hr * WM_BM + r) * QS + ch * 8) = v;
   }
-  {
-    const float a1 = r1[h], a2 = r2[h], a3 = pb[h];
-    for (int i = tid; i < window; i += 128) tab[i] = a1 * log1pf(a2 * static_cast<float>(i)) - a3;
+  // log2(e) * (r1 ln(1 + r2 dist) - pb): the weight is 1 / (1 + 2^(tab[dist] - log2(e) scale s))
+  for (int i = tid; i < REPB * window; i += NT) {
+    const int h = h0 + i / window, dist = i % window;
+    tab[i] = LOG2E * (r1[h] * log1pf(r2[h] * static_cast<float>(dist)) - pb[h]);
   }
+  const float scale2 = scale * LOG2E;
   const int t_hi = min(len - 1, t0 + WM_BM - 1);
   const int j_lo = max(0, pos0 + t0 - window + 1), j_hi = pos0 + t_hi;
-  const int row_lo = warp * 16 + (lane >> 2);
+  const int row_lo = wr * 16 + (lane >> 2);
   const int p_lo = pos0 + t0 + row_lo, p_hi = p_lo + 8;
   const bool ok_lo = t0 + row_lo < len, ok_hi = t0 + row_lo + 8 < len;
+  const float* mytab = tab + hw * window;
   float oacc[DV / 8][4];
 #pragma unroll
   for (int i = 0; i < DV / 8; ++i)
 #pragma unroll
     for (int e = 0; e < 4; ++e) oacc[i][e] = 0.f;
 
-  for (int j0 = j_lo; j0 <= j_hi; j0 += WM_BN) {
-    __syncthreads();
-    for (int idx = tid; idx < WM_BN * (D / 8); idx += 128) {
+  auto load_tile = [&](int stage, int j0) {
+    __nv_bfloat16* kd = Ks + stage * WM_BN * QS;
+    __nv_bfloat16* vd = Vs + stage * WM_BN * VS;
+    for (int idx = tid; idx < WM_BN * (D / 8); idx += NT) {
       const int key = idx / (D / 8), ch = idx % (D / 8), j = j0 + key;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (j <= j_hi) v = ldg_v4(k_cache + (static_cast<size_t>(bt[j / page]) * page + j % page) * G * D + g * D + ch * 8);
-      *reinterpret_cast<uint4*>(Ks + key * QS + ch * 8) = v;
+      const bool ok = j <= j_hi;
+      size_t slot = 0;
+      if (ok) {
+        const int pg = page_shift >= 0 ? j >> page_shift : j / page;
+        slot = static_cast<size_t>(bt[pg]) * page + (j - pg * page);
+      }
+      cp_async_16(kd + key * QS + ch * 8, k_cache + (slot * G + g) * D + ch * 8, ok);
+      cp_async_16(vd + key * VS + ch * 8, v_cache + (slot * G + g) * DV + ch * 8, ok);
     }
-    for (int idx = tid; idx < WM_BN * (DV / 8); idx += 128) {
-      const int key = idx / (DV / 8), ch = idx % (DV / 8), j = j0 + key;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (j <= j_hi) v = ldg_v4(v_cache + (static_cast<size_t>(bt[j / page]) * page + j % page) * G * DV + g * DV + ch * 8);
-      *reinterpret_cast<uint4*>(Vs + key * VS + ch * 8) = v;
-    }
-    __syncthreads();
+  };
+  const int n_tiles = (j_hi - j_lo) / WM_BN + 1;
+  load_tile(0, j_lo);
+  cp_async_commit();
+  for (int t = 0; t < n_tiles; ++t) {
+    const int j0 = j_lo + t * WM_BN;
+    cp_async_wait<0>();
+    __syncthreads();                                 // tile t has landed (Q and the table too); tile t - 1 is consumed
+    if (t + 1 < n_tiles) load_tile((t + 1) & 1, j0 + WM_BN);
+    cp_async_commit();
+    const __nv_bfloat16* Kt = Ks + (t & 1) * WM_BN * QS;
+    const __nv_bfloat16* Vt = Vs + (t & 1) * WM_BN * VS;
     // this warp's rows see keys p - window + 1 .. p: skip a tile none of its 16 rows can see
-    const int wp_lo = pos0 + t0 + warp * 16, wp_hi = wp_lo + 15;
-    if (j0 > wp_hi || j0 + WM_BN - 1 < wp_lo - window + 1 || t0 + warp * 16 >= len) continue;
+    const int wp_lo = pos0 + t0 + wr * 16, wp_hi = wp_lo + 15;
+    if (j0 > wp_hi || j0 + WM_BN - 1 < wp_lo - window + 1 || t0 + wr * 16 >= len) continue;
     float sacc[WM_BN / 8][4];
 #pragma unroll
     for (int i = 0; i < WM_BN / 8; ++i)
@@ -423,24 +430,26 @@ window_sigmoid_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_b
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) {
       uint32_t a[4];
-      ldsm_x4(a[0], a[1], a[2], a[3], Qs + (warp * 16 + (lane & 15)) * QS + ks * 16 + (lane >> 4) * 8);
+      ldsm_x4(a[0], a[1], a[2], a[3], Qs + (hw * WM_BM + wr * 16 + (lane & 15)) * QS + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
       for (int np = 0; np < WM_BN / 16; ++np) {
         uint32_t b0, b1, b2, b3;
-        ldsm_x4(b0, b1, b2, b3, Ks + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * QS + ks * 16 + ((lane >> 3) & 1) * 8);
+        ldsm_x4(b0, b1, b2, b3, Kt + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * QS + ks * 16 + ((lane >> 3) & 1) * 8);
         mma_bf16_16816(sacc[2 * np], a, b0, b1);
         mma_bf16_16816(sacc[2 * np + 1], a, b2, b3);
       }
     }
+    // a tile wholly inside every row's window needs no per-element test
+    const bool inner = j0 + WM_BN - 1 <= wp_lo && j0 >= wp_hi - window + 1 && t0 + wr * 16 + 15 < len;
 #pragma unroll
     for (int nt = 0; nt < WM_BN / 8; ++nt) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int j = j0 + nt * 8 + 2 * (lane & 3) + (e & 1);
         const int dist = (e < 2 ? p_lo : p_hi) - j;
-        const bool ok = (e < 2 ? ok_lo : ok_hi) && dist >= 0 && dist < window;
+        const bool ok = inner || ((e < 2 ? ok_lo : ok_hi) && dist >= 0 && dist < window);
         float w = 0.f;
-        if (ok) w = __frcp_rn(1.0f + __expf(tab[dist] - sacc[nt][e] * scale));
+        if (ok) w = __fdividef(1.0f, 1.0f + exp2f(mytab[dist] - sacc[nt][e] * scale2));
         sacc[nt][e] = w;
       }
     }
@@ -454,7 +463,7 @@ window_sigmoid_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_b
 #pragma unroll
       for (int np = 0; np < DV / 16; ++np) {
         uint32_t b0, b1, b2, b3;
-        ldsm_x4_t(b0, b1, b2, b3, Vs + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * VS + np * 16 + (lane >> 4) * 8);
+        ldsm_x4_t(b0, b1, b2, b3, Vt + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * VS + np * 16 + (lane >> 4) * 8);
         mma_bf16_16816(oacc[2 * np], ah, b0, b1);
         mma_bf16_16816(oacc[2 * np], al, b0, b1);
         mma_bf16_16816(oacc[2 * np + 1], ah, b2, b3);
@@ -462,28 +471,34 @@ window_sigmoid_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_b
       }
     }
   }
+  cp_async_wait<0>();
 #pragma unroll
   for (int half = 0; half < 2; ++half) {
     if (!(half ? ok_hi : ok_lo)) continue;
-    __nv_bfloat16* o = out + static_cast<size_t>(start + t0 + row_lo + 8 * half) * H * DV + h * DV + 2 * (lane & 3);
+    __nv_bfloat16* o = out + static_cast<size_t>(start + t0 + row_lo + 8 * half) * H * DV + (h0 + hw) * DV + 2 * (lane & 3);
 #pragma unroll
     for (int nt = 0; nt < DV / 8; ++nt)
       *reinterpret_cast<uint32_t*>(o + nt * 8) = pack_bf16(oacc[nt][2 * half], oacc[nt][2 * half + 1]);
   }
 }
 
-template <int D>
-static cudaError_t launch_window_mma(dim3 grid, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
+template <int D, int REPB>
+static cudaError_t launch_window_mma(int max_new, int n_seqs, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
                                      const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* bt,
                                      int bt_stride, const float* r1, const float* r2, const float* pb, int H, int G, int page,
                                      int window, float scale) {
-  auto kern = window_sigmoid_attn_mma_kernel<D, D>;
-  const size_t smem = sizeof(__nv_bfloat16) * (2 * WM_BM * (D + 8) + WM_BN * (D + 8)) + sizeof(float) * window;
+  auto kern = window_sigmoid_attn_mma_kernel<D, D, REPB>;
+  const size_t smem = sizeof(__nv_bfloat16) * (REPB * WM_BM + 4 * WM_BN) * (D + 8) + sizeof(float) * REPB * window;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   if (e != cudaSuccess) return e;
   using B = __nv_bfloat16;
-  kern<<<grid, 128, smem, st>>>(static_cast<const B*>(q), static_cast<const B*>(kc), static_cast<const B*>(vc), static_cast<B*>(out),
-                                seq_start, seq_pos0, seq_len, bt, bt_stride, r1, r2, pb, H, G, page, window, scale);
+  int page_shift = -1;
+  if ((page & (page - 1)) == 0)
+    for (page_shift = 0; (1 << page_shift) < page; ++page_shift) {}
+  const dim3 grid((max_new + WM_BM - 1) / WM_BM, H / REPB, n_seqs);
+  kern<<<grid, 128 * REPB, smem, st>>>(static_cast<const B*>(q), static_cast<const B*>(kc), static_cast<const B*>(vc),
+                                       static_cast<B*>(out), seq_start, seq_pos0, seq_len, bt, bt_stride, r1, r2, pb, H, G, page,
+                                       page_shift, window, scale);
   return cudaSuccess;
 }
 
@@ -553,9 +568,12 @@ extern "C" int b2tts_window_sigmoid_attn(const void* q, const void* k_cache, con
   }
   // prompt portions in bf16 with a supported head size: the tensor-core kernel
   if (stream_ok && dtype == B2TTS_DTYPE_BF16 && dim == vdim && (dim == 32 || dim == 64 || dim == 96 || dim == 128) && window <= 8192) {
-    const dim3 grid_m((max_new + WM_BM - 1) / WM_BM, heads, n_seqs);
-#define WM_GO(DD) e = launch_window_mma<DD>(grid_m, st, q, k_cache, v_cache, out, seq_start, seq_pos0, seq_len, block_tables, bt_stride, \
-                                            r1, r2, pb, heads, kv_heads, page, window, scale)
+    // two heads of a key/value group per CTA when the group is even and both distance tables fit
+    const bool two = rep % 2 == 0 && window <= 4096;
+#define WM_GO(DD) e = two ? launch_window_mma<DD, 2>(max_new, n_seqs, st, q, k_cache, v_cache, out, seq_start, seq_pos0, seq_len, \
+                                                     block_tables, bt_stride, r1, r2, pb, heads, kv_heads, page, window, scale)  \
+                          : launch_window_mma<DD, 1>(max_new, n_seqs, st, q, k_cache, v_cache, out, seq_start, seq_pos0, seq_len, \
+                                                     block_tables, bt_stride, r1, r2, pb, heads, kv_heads, page, window, scale)
     if (dim == 32) WM_GO(32); else if (dim == 64) WM_GO(64); else if (dim == 96) WM_GO(96); else WM_GO(128);
 #undef WM_GO
     if (e != cudaSuccess) return cuda_fail(e, "window_sigmoid_attn (tensor)");

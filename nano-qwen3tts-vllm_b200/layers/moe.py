@@ -3,7 +3,9 @@
 Router logits are computed in float; the ``top`` experts with the largest sigmoid scores are chosen, and their
 weights are the scores divided by their sum (+ 1e-20) times ``scale``.  Experts are two-matrix feed-forwards with a
 squared-ReLU activation, stored stacked ([experts, ff, width] / [experts, width, ff]) so that ONE grouped launch runs
-all of them over the (token, choice) pairs sorted by expert.  ``forward`` returns the per-pair outputs and weights;
+all of them over the (token, choice) pairs sorted by expert - for a prompt portion of thousands of tokens and for a
+decode step of a few rows per expert alike, with no group size ever read back to the host.  ``forward`` returns the
+per-pair outputs and weights;
 the weighted sum over a token's choices is taken, in a fixed order, by the residual kernel that consumes them."""
 import torch
 from torch import nn
@@ -28,38 +30,13 @@ class SigmoidTopKMoE(nn.Module):
         nat.moe_route(h, self.router, top_idx, top_w, offsets, sorted_pair, self.top, self.scale)
         return top_idx, top_w, offsets, sorted_pair
 
-    # (token, choice) pairs from which the experts run as one library GEMM each over their gathered rows (compute-bound
-    # prompt portions); below it - decoding - the one grouped launch serves all experts and nothing waits on the host
-    SORTED_GEMM_MIN_PAIRS = 2048
-
     def forward(self, h: torch.Tensor):
         """h [n, width] -> (z [n * top, width], weights [n, top]): z[t * top + k] is the output of token t's k-th expert."""
         n = h.shape[0]
         pairs = n * self.top
         _, top_w, offsets, sorted_pair = self.route(h)
-        if pairs >= self.SORTED_GEMM_MIN_PAIRS and not torch.cuda.is_current_stream_capturing():
-            return self._sorted_gemms(h, offsets, sorted_pair, pairs), top_w
         y = torch.empty(pairs, self.ff, dtype=h.dtype, device=h.device)
         nat.grouped_gemm(h, self.up, y, offsets, sorted_pair, pairs, self.top, in_by_token=True, out_by_pair=False, act=1)
         z = torch.empty(pairs, self.width, dtype=h.dtype, device=h.device)
         nat.grouped_gemm(y, self.down, z, offsets, sorted_pair, pairs, self.top, in_by_token=False, out_by_pair=True, act=0)
         return z, top_w
-
-    def _sorted_gemms(self, h, offsets, sorted_pair, pairs):
-        """Rows gathered in expert order, one GEMM pair per expert over its contiguous slice (the group sizes are read
-        back: one host synchronisation per layer), results scattered back to (token, choice) order."""
-        from .linear import linear
-        xs = nat.permute_rows(h, torch.empty(pairs, self.width, dtype=h.dtype, device=h.device), sorted_pair, div=self.top)
-        bounds = offsets.tolist()
-        y = torch.empty(pairs, self.ff, dtype=h.dtype, device=h.device)
-        for e in range(self.experts):
-            lo, hi = bounds[e], bounds[e + 1]
-            if hi > lo:
-                linear(xs[lo:hi], self.up[e], out=y[lo:hi])
-        nat.relu_sq_(y)
-        zs = xs                                             # the gathered inputs are dead: reuse their rows
-        for e in range(self.experts):
-            lo, hi = bounds[e], bounds[e + 1]
-            if hi > lo:
-                linear(y[lo:hi], self.down[e], out=zs[lo:hi])
-        return nat.permute_rows(zs, torch.empty(pairs, self.width, dtype=h.dtype, device=h.device), sorted_pair, scatter=True)
