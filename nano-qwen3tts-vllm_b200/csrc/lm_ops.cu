@@ -225,10 +225,8 @@ template <> struct Vec4<__nv_bfloat16> {
 constexpr int CONV4_CHUNKS = 2;            // head sizes up to 256
 constexpr int CONV4_TOKENS = 8;            // consecutive rows of the step per warp: the taps' weights are loaded once for all
 
-// One warp per (block of CONV4_TOKENS rows, head slice).  The lane keeps the taps of its four channels in registers and
-// walks the rows; a row's earlier taps were the previous rows' loads (same addresses: they hit in L1), so u is read
-// from memory about once.
-template <typename T, int TAPS>
+// One warp per (block of CONV4_TOKENS rows, head slice).  The lane keeps the taps of its four channels in registers.
+template <typename T, int TAPS, int NCH>
 __global__ void __launch_bounds__(CONV_WARPS * 32)
 conv_headnorm_kvwrite_vec4_kernel(const T* __restrict__ u, int64_t u_stride, const float* __restrict__ conv_w,
                                   const T* __restrict__ state, const int32_t* __restrict__ tok_seq,
@@ -249,10 +247,10 @@ conv_headnorm_kvwrite_vec4_kernel(const T* __restrict__ u, int64_t u_stride, con
   else if (hs < H + G) { kind = 1; head = hs - H; width = d; c0 = H * d + head * d; }
   else { kind = 2; head = hs - H - G; width = dv; c0 = H * d + G * d + head * dv; }
   constexpr int R = TAPS - 1;
-  float w[CONV4_CHUNKS][4][TAPS];
-  float g4[CONV4_CHUNKS][4];
+  float w[NCH][4][TAPS];
+  float g4[NCH][4];
 #pragma unroll
-  for (int i = 0; i < CONV4_CHUNKS; ++i) {
+  for (int i = 0; i < NCH; ++i) {
     const int cc = (lane + 32 * i) * 4;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
@@ -281,6 +279,67 @@ conv_headnorm_kvwrite_vec4_kernel(const T* __restrict__ u, int64_t u_stride, con
       m_pos0 = seq_pos0[b]; m_start = seq_start[b]; m_sslot = seq_slot[b];
     }
   }
+  // norm of a q / k head (the convolution's output rounded to T first), then the row's destination
+  auto finish = [&](float (&y)[NCH][4], int n, int slot) {
+    if (kind != 2) {
+      float ssq = 0.f;
+#pragma unroll
+      for (int i = 0; i < NCH; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { y[i][e] = to_f(from_f<T>(y[i][e])); ssq += y[i][e] * y[i][e]; }
+      ssq = warp_sum(ssq);
+      const float inv = 1.0f / sqrtf(ssq / static_cast<float>(width) + eps);
+#pragma unroll
+      for (int i = 0; i < NCH; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) y[i][e] *= inv * g4[i][e];
+    }
+    T* dst = kind == 0 ? q_out + static_cast<size_t>(n) * H * d + head * d
+           : kind == 1 ? k_cache + static_cast<size_t>(slot) * G * d + head * d
+                       : v_cache + static_cast<size_t>(slot) * G * dv + head * dv;
+#pragma unroll
+    for (int i = 0; i < NCH; ++i) {
+      const int cc = (lane + 32 * i) * 4;
+      if (cc < width) Vec4<T>::store(dst + cc, y[i]);
+    }
+  };
+  // The usual block of a prompt portion: CONV4_TOKENS consecutive tokens of one sequence.  Their projections and the
+  // taps - 1 before the first are loaded once, all loads issued before the first use; row t then reads entries t .. t + R.
+  const int p0 = __shfl_sync(0xffffffffu, m_p, 0), start0 = __shfl_sync(0xffffffffu, m_start, 0);
+  const bool mine = lane >= CONV4_TOKENS || (m_slot >= 0 && m_start == start0 && m_p == p0 + lane);
+  if (__all_sync(0xffffffffu, mine)) {
+    const int pos0 = __shfl_sync(0xffffffffu, m_pos0, 0), sslot = __shfl_sync(0xffffffffu, m_sslot, 0);
+    float uv[CONV4_TOKENS + R][NCH][4];
+#pragma unroll
+    for (int k = 0; k < CONV4_TOKENS + R; ++k) {
+      const int pk = p0 - R + k;
+#pragma unroll
+      for (int i = 0; i < NCH; ++i) {
+        const int cc = (lane + 32 * i) * 4;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) uv[k][i][e] = 0.f;             // before the sequence's start
+        if (cc < width) {
+          if (pk >= pos0) Vec4<T>::load(u + static_cast<int64_t>(start0 + pk - pos0) * u_stride + c0 + cc, uv[k][i]);
+          else if (pk >= 0) Vec4<T>::load(state + (static_cast<size_t>(sslot) * R + (pk - (pos0 - R))) * C + c0 + cc, uv[k][i]);
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < CONV4_TOKENS; ++t) {
+      float y[NCH][4];
+#pragma unroll
+      for (int i = 0; i < NCH; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          y[i][e] = 0.f;
+#pragma unroll
+          for (int j = 0; j < TAPS; ++j) y[i][e] = fmaf(w[i][e][j], uv[t + j][i][e], y[i][e]);
+        }
+      finish(y, n0 + t, __shfl_sync(0xffffffffu, m_slot, t));
+    }
+    return;
+  }
+  // anything else (decoded tokens, the seam of two sequences, padding): row by row
 #pragma unroll
   for (int t = 0; t < CONV4_TOKENS; ++t) {
     const int n = n0 + t;
@@ -296,9 +355,9 @@ conv_headnorm_kvwrite_vec4_kernel(const T* __restrict__ u, int64_t u_stride, con
       if (pj >= pos0) src[j] = u + static_cast<int64_t>(start + pj - pos0) * u_stride;
       else if (pj >= 0) src[j] = state + (static_cast<size_t>(sslot) * R + (pj - (pos0 - R))) * C;
     }
-    float y[CONV4_CHUNKS][4];
+    float y[NCH][4];
 #pragma unroll
-    for (int i = 0; i < CONV4_CHUNKS; ++i) {
+    for (int i = 0; i < NCH; ++i) {
       const int cc = (lane + 32 * i) * 4;
 #pragma unroll
       for (int e = 0; e < 4; ++e) y[i][e] = 0.f;
@@ -314,27 +373,7 @@ conv_headnorm_kvwrite_vec4_kernel(const T* __restrict__ u, int64_t u_stride, con
         }
       }
     }
-    if (kind != 2) {
-      float ssq = 0.f;
-#pragma unroll
-      for (int i = 0; i < CONV4_CHUNKS; ++i)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) { y[i][e] = to_f(from_f<T>(y[i][e])); ssq += y[i][e] * y[i][e]; }
-      ssq = warp_sum(ssq);
-      const float inv = 1.0f / sqrtf(ssq / static_cast<float>(width) + eps);
-#pragma unroll
-      for (int i = 0; i < CONV4_CHUNKS; ++i)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) y[i][e] *= inv * g4[i][e];
-    }
-    T* dst = kind == 0 ? q_out + static_cast<size_t>(n) * H * d + head * d
-           : kind == 1 ? k_cache + static_cast<size_t>(slot) * G * d + head * d
-                       : v_cache + static_cast<size_t>(slot) * G * dv + head * dv;
-#pragma unroll
-    for (int i = 0; i < CONV4_CHUNKS; ++i) {
-      const int cc = (lane + 32 * i) * 4;
-      if (cc < width) Vec4<T>::store(dst + cc, y[i]);
-    }
+    finish(y, n, slot);
   }
 }
 
@@ -447,9 +486,10 @@ static void launch_conv(bool vec4, int grid, cudaStream_t st, const void* u, int
                         const int32_t* seq_len, const int32_t* seq_slot, const int32_t* slot_mapping, const float* q_norm_w,
                         const float* k_norm_w, void* q_out, void* k_cache, void* v_cache, int n_tokens, int n_seqs, int H, int G, int d,
                         int dv, int taps, float eps, int C) {
-#define CONV4_GO(TP) conv_headnorm_kvwrite_vec4_kernel<T, TP><<<grid, CONV_WARPS * 32, 0, st>>>(static_cast<const T*>(u), u_stride, conv_w, \
+#define CONV4_GO_N(TP, NCH) conv_headnorm_kvwrite_vec4_kernel<T, TP, NCH><<<grid, CONV_WARPS * 32, 0, st>>>(static_cast<const T*>(u), u_stride, conv_w, \
       static_cast<const T*>(state), tok_seq, positions, seq_start, seq_pos0, seq_slot, slot_mapping, q_norm_w, k_norm_w, \
       static_cast<T*>(q_out), static_cast<T*>(k_cache), static_cast<T*>(v_cache), n_tokens, H, G, d, dv, eps)
+#define CONV4_GO(TP) do { if (d <= 128 && dv <= 128) CONV4_GO_N(TP, 1); else CONV4_GO_N(TP, 2); } while (0)
   if (vec4) grid = ((n_tokens + CONV4_TOKENS - 1) / CONV4_TOKENS * (H + 2 * G) + CONV_WARPS - 1) / CONV_WARPS;
   if (vec4 && taps == 4) CONV4_GO(4);
   else if (vec4 && taps == 3) CONV4_GO(3);
@@ -460,6 +500,7 @@ static void launch_conv(bool vec4, int grid, cudaStream_t st, const void* u, int
         tok_seq, positions, seq_start, seq_pos0, seq_slot, slot_mapping, q_norm_w, k_norm_w, static_cast<T*>(q_out),
         static_cast<T*>(k_cache), static_cast<T*>(v_cache), n_tokens, H, G, d, dv, taps, eps);
 #undef CONV4_GO
+#undef CONV4_GO_N
   if (taps > 1)
     conv_state_update_kernel<T><<<dim3((C + 127) / 128, n_seqs), 128, 0, st>>>(static_cast<const T*>(u), u_stride, static_cast<T*>(state),
         seq_start, seq_pos0, seq_len, seq_slot, n_seqs, C, taps);

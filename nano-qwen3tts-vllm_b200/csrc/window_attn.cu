@@ -217,7 +217,7 @@ window_sigmoid_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__
                                   const int32_t* __restrict__ seq_pos0, const int32_t* __restrict__ seq_len,
                                   const int32_t* __restrict__ block_tables, int bt_stride, const float* __restrict__ r1,
                                   const float* __restrict__ r2, const float* __restrict__ pb, int H, int G, int d, int dv,
-                                  int page, int window, float scale) {
+                                  int page, int window, float scale, int use_tab) {
   constexpr int VEC = WdVec<T>::N;
   constexpr int KPI = 32 / LPK;                      // keys per warp load
   extern __shared__ __align__(16) float red[];       // [WD_WARPS][rep][dv]
@@ -250,6 +250,17 @@ window_sigmoid_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__
   int32_t* pages = reinterpret_cast<int32_t*>(red + WD_WARPS * rep * dv);
   const int pg0 = j_lo / page;
   for (int i = threadIdx.x; i <= p / page - pg0; i += blockDim.x) pages[i] = bt[pg0 + i];
+  // the heads' distance terms, once per CTA instead of once per lane and key:
+  //   tab[r][dist] = log2(e) (r1 ln(1 + r2 dist) - pb),  weight = 1 / (1 + 2^(tab - log2(e) scale s))
+  constexpr float LOG2E = 1.4426950408889634f;
+  const int span = p - j_lo + 1;
+  float* tab = reinterpret_cast<float*>(pages + (window + page - 1) / page + 2);
+  if (use_tab)
+    for (int i = threadIdx.x; i < rep * span; i += blockDim.x) {
+      const int r = i / span, h = g * rep + r;
+      tab[i] = LOG2E * (r1[h] * log1pf(r2[h] * static_cast<float>(i - r * span)) - pb[h]);
+    }
+  const float scale2 = scale * LOG2E;
   __syncthreads();
   for (int base = j_lo + warp * KPI * WD_UNROLL; base <= p; base += WD_WARPS * KPI * WD_UNROLL) {
     uint4 kr[WD_UNROLL], vr[WD_UNROLL];
@@ -281,8 +292,12 @@ window_sigmoid_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__
         for (int o = LPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         float w = 0.f;
         if (j <= p && r < rep) {
-          const float z = s * scale - hr1[r] * log1pf(hr2[r] * dist) + hpb[r];
-          w = 1.0f / (1.0f + expf(-z));
+          if (use_tab) {
+            w = __fdividef(1.0f, 1.0f + exp2f(tab[r * span + (p - j)] - s * scale2));
+          } else {
+            const float z = s * scale - hr1[r] * log1pf(hr2[r] * dist) + hpb[r];
+            w = 1.0f / (1.0f + expf(-z));
+          }
         }
 #pragma unroll
         for (int i = 0; i < VEC; ++i) acc[r][i] = fmaf(w, vf[i], acc[r][i]);
@@ -316,7 +331,7 @@ template <typename T, int LPK, int REP>
 static cudaError_t launch_window_decode(dim3 grid, size_t smem, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
                                         const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len, const int32_t* bt,
                                         int bt_stride, const float* r1, const float* r2, const float* pb, int H, int G, int d, int dv,
-                                        int page, int window, float scale) {
+                                        int page, int window, float scale, int use_tab) {
   auto kern = window_sigmoid_attn_decode_kernel<T, LPK, REP>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -324,7 +339,7 @@ static cudaError_t launch_window_decode(dim3 grid, size_t smem, cudaStream_t st,
   }
   kern<<<grid, WD_WARPS * 32, smem, st>>>(static_cast<const T*>(q), static_cast<const T*>(kc), static_cast<const T*>(vc),
                                           static_cast<T*>(out), seq_start, seq_pos0, seq_len, bt, bt_stride, r1, r2, pb, H, G, d, dv,
-                                          page, window, scale);
+                                          page, window, scale, use_tab);
   return cudaSuccess;
 }
 
@@ -506,9 +521,9 @@ template <typename T, int LPK>
 static cudaError_t launch_window_decode_rep(int rep, dim3 grid, size_t smem, cudaStream_t st, const void* q, const void* kc, const void* vc,
                                             void* out, const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len,
                                             const int32_t* bt, int bt_stride, const float* r1, const float* r2, const float* pb, int H,
-                                            int G, int d, int dv, int page, int window, float scale) {
+                                            int G, int d, int dv, int page, int window, float scale, int use_tab) {
 #define WD_GO(R) launch_window_decode<T, LPK, R>(grid, smem, st, q, kc, vc, out, seq_start, seq_pos0, seq_len, bt, bt_stride, r1, r2, pb, \
-                                                 H, G, d, dv, page, window, scale)
+                                                 H, G, d, dv, page, window, scale, use_tab)
   if (rep <= 1) return WD_GO(1);
   if (rep <= 2) return WD_GO(2);
   if (rep <= 4) return WD_GO(4);
@@ -520,9 +535,10 @@ template <typename T>
 static cudaError_t launch_window_decode_any(int lpk, int rep, dim3 grid, size_t smem, cudaStream_t st, const void* q, const void* kc,
                                             const void* vc, void* out, const int32_t* seq_start, const int32_t* seq_pos0,
                                             const int32_t* seq_len, const int32_t* bt, int bt_stride, const float* r1, const float* r2,
-                                            const float* pb, int H, int G, int d, int dv, int page, int window, float scale) {
+                                            const float* pb, int H, int G, int d, int dv, int page, int window, float scale,
+                                            int use_tab) {
 #define WD_GO(L) launch_window_decode_rep<T, L>(rep, grid, smem, st, q, kc, vc, out, seq_start, seq_pos0, seq_len, bt, bt_stride, r1, r2, \
-                                                pb, H, G, d, dv, page, window, scale)
+                                                pb, H, G, d, dv, page, window, scale, use_tab)
   if (lpk <= 8) return WD_GO(8);
   if (lpk <= 16) return WD_GO(16);
   return WD_GO(32);
@@ -554,14 +570,17 @@ extern "C" int b2tts_window_sigmoid_attn(const void* q, const void* k_cache, con
                          aligned16(v_cache);
   if (stream_ok) {
     const int lpk = (widest + vec - 1) / vec;
-    const size_t smem_d = sizeof(float) * WD_WARPS * rep * vdim + sizeof(int32_t) * ((window + page - 1) / page + 2);
+    const size_t tab_bytes = sizeof(float) * rep * window;
+    const int use_tab = tab_bytes <= 64 * 1024;          // larger windows compute the distance term per key
+    const size_t smem_d = sizeof(float) * WD_WARPS * rep * vdim + sizeof(int32_t) * ((window + page - 1) / page + 2) +
+                          (use_tab ? tab_bytes : 0);
     const dim3 grid_d(1, kv_heads, n_seqs);
     if (dtype == B2TTS_DTYPE_BF16)
       e = launch_window_decode_any<__nv_bfloat16>(lpk, rep, grid_d, smem_d, st, q, k_cache, v_cache, out, seq_start, seq_pos0, seq_len,
-                                                  block_tables, bt_stride, r1, r2, pb, heads, kv_heads, dim, vdim, page, window, scale);
+                                                  block_tables, bt_stride, r1, r2, pb, heads, kv_heads, dim, vdim, page, window, scale, use_tab);
     else
       e = launch_window_decode_any<float>(lpk, rep, grid_d, smem_d, st, q, k_cache, v_cache, out, seq_start, seq_pos0, seq_len,
-                                          block_tables, bt_stride, r1, r2, pb, heads, kv_heads, dim, vdim, page, window, scale);
+                                          block_tables, bt_stride, r1, r2, pb, heads, kv_heads, dim, vdim, page, window, scale, use_tab);
     if (e != cudaSuccess) return cuda_fail(e, "window_sigmoid_attn (streaming)");
     B2_CHECK_LAUNCH("window_sigmoid_attn (streaming)");
     if (max_new == 1) return B2TTS_OK;
