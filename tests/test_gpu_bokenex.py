@@ -223,6 +223,22 @@ def test_bfloat16_window_edge_key_dominates(nat, window, page):
                 assert rel(out, ref) < 1e-2
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 1e-2)])
+def test_far_key_among_hundreds(nat, dtype, tol):
+    """A dominating key 699 or 700 positions back, behind hundreds of ordinary keys and a dozen page borders, with a
+    window of 700: seen at distance 699 and not at 700, by a single decoded token, by a short portion and by a portion
+    longer than a query tile that starts in the middle of the context."""
+    window, page, j = 700, 64, 37
+    for i in (j + window - 1, j + window):
+        for cached, new in ((i, 1), (i - 1, 3), (i - 100, 130)):
+            out, ref = _attn_case(nat, 4, 2, 32, 32, window, page, [(cached, new), (5, 1)], dtype=dtype, spike=(0, j), seed=i)
+            row = i - cached
+            seen = ref[row].abs().max().item() > 500
+            assert seen == (i - j < window)
+            assert (out[row].float().abs().max().item() > 500) == seen
+            assert rel(out, ref) < tol
+
+
 @pytest.mark.parametrize("cols,ff,n", [(72, 136, 700), (64, 40, 300), (256, 128, 5)])
 def test_grouped_experts_on_the_tensor_cores(nat, cols, ff, n):
     """Groups longer than one 128-row tile, inner sizes with a tail slice, more than one column tile, a handful of rows,
