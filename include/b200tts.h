@@ -246,6 +246,8 @@ B2TTS_API int b2tts_frame_advance(const int64_t* code0, int eos_id, int32_t* act
  *                                              out may alias residual)
  *           B2TTS_GEMM_SILU_MUL  out[m, n/2] = silu(bf16(gate)) * bf16(up)   (qwen3_tts_share.py:131-135;
  *                                              `rounding` as b2tts_silu_and_mul)
+ *           B2TTS_GEMM_RELU_SQ   out[m, n]   = bf16(max(bf16(acc), 0)^2)      (squared-ReLU feed-forwards; single-GEMM
+ *                                              entry points only)
  * splits: K-split = cluster size (1,2,4,8,16; 0 = choose so that tiles * splits fill the SMs); the
  * partial sums are exchanged through distributed shared memory and added in a fixed order.
  * splits = -2 / -4: the cluster splits the BATCH instead (m padded to 16 must be a multiple of 32 / 64, m <= 128):
@@ -258,6 +260,7 @@ B2TTS_API int b2tts_frame_advance(const int64_t* code0, int eos_id, int32_t* act
 #define B2TTS_GEMM_BIAS     0
 #define B2TTS_GEMM_RESIDUAL 1
 #define B2TTS_GEMM_SILU_MUL 2
+#define B2TTS_GEMM_RELU_SQ  3
 #define B2TTS_PACK_PLAIN    0
 #define B2TTS_PACK_GATE_UP  1
 B2TTS_API int    b2tts_gemm_bf16_supported(int m, int n, int k);

@@ -422,7 +422,7 @@ def frame_advance(code0, eos_id, active, seq_lens, gen_step, frames_done, extra_
 
 
 # ------------------------------------------------------------------------------------------ a7
-GEMM_BIAS, GEMM_RESIDUAL, GEMM_SILU_MUL = 0, 1, 2
+GEMM_BIAS, GEMM_RESIDUAL, GEMM_SILU_MUL, GEMM_RELU_SQ = 0, 1, 2, 3
 PACK_PLAIN, PACK_GATE_UP = 0, 1
 GEMM_MAX_M = 1 << 16        # any batch: rows beyond 128 run as 128-row chunks of the same kernel (gemm.cu)
 GEMM_CHAIN_MAX_M = 128

@@ -428,6 +428,10 @@ gemm_stream_kernel(const GemmParams p, const __grid_constant__ CUtensorMap tmap_
         const uint4 bw = have_pre ? pre : ldg_v4(p.bias + n);
         acc[0] += bf16lo(bw.x); acc[1] += bf16hi(bw.x); acc[2] += bf16lo(bw.y); acc[3] += bf16hi(bw.y);
         acc[4] += bf16lo(bw.z); acc[5] += bf16hi(bw.z); acc[6] += bf16lo(bw.w); acc[7] += bf16hi(bw.w);
+      } else if (p.epilogue == B2TTS_GEMM_RELU_SQ) {
+        // bf16(max(bf16(x W^T), 0)^2): the activation of a two-matrix feed-forward on the rounded projection
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { const float r = fmaxf(rbf(acc[j]), 0.f); acc[j] = r * r; }
       } else if (p.epilogue == B2TTS_GEMM_RESIDUAL) {
         // bf16(residual + bf16(x W^T)): the projection output is rounded before the add
         const uint4 rw = have_pre ? pre : ldg_v4(p.res + (int64_t)(row0 + m) * p.res_stride + n);
@@ -688,8 +692,8 @@ static int gemm_impl(const char* what, const void* x, int64_t x_row_stride, cons
   B2_REQUIRE(b2tts_gemm_bf16_supported(m, n, k), B2TTS_EUNSUPPORTED,
              "%s: m=%d (1..%d), n=%d (multiple of %d), k=%d (multiple of %d)", what, m, G_MAX_ROWS, n, G_BN, k, G_BK);
   B2_REQUIRE(x && w_packed && out, B2TTS_EINVAL, "%s: null pointer", what);
-  B2_REQUIRE(epilogue == B2TTS_GEMM_BIAS || epilogue == B2TTS_GEMM_RESIDUAL || epilogue == B2TTS_GEMM_SILU_MUL,
-             B2TTS_EINVAL, "%s: epilogue %d", what, epilogue);
+  B2_REQUIRE(epilogue == B2TTS_GEMM_BIAS || epilogue == B2TTS_GEMM_RESIDUAL || epilogue == B2TTS_GEMM_SILU_MUL ||
+                 epilogue == B2TTS_GEMM_RELU_SQ, B2TTS_EINVAL, "%s: epilogue %d", what, epilogue);
   B2_REQUIRE(epilogue != B2TTS_GEMM_RESIDUAL || residual, B2TTS_EINVAL, "%s: residual epilogue without residual", what);
   B2_REQUIRE(aligned16(x) && aligned16(w_packed) && aligned16(out) && x_row_stride % 8 == 0 && out_row_stride % 4 == 0 &&
                  (epilogue == B2TTS_GEMM_SILU_MUL || out_row_stride % 8 == 0) &&

@@ -184,13 +184,15 @@ static cudaError_t launch_window_attn(dim3 grid, size_t smem, cudaStream_t st, c
 
 // ------------------------------------------------------------------ one new token per sequence: stream the window once
 // One CTA per (sequence, key/value head), 8 warps.  A key is read by LPK lanes, 16 bytes each, so a warp takes 32 / LPK
-// keys per load instruction and four such groups per iteration: all eight loads are issued, as raw 16-byte registers,
-// before the first use, and the pages of the window are looked up once per CTA into shared memory.  The
-// lane's slice of q stays in registers for every head of the group; a score is a dot over the slice plus log2(LPK)
-// shuffles; the weighted values accumulate per lane and are summed over key groups and warps at the end, in a fixed
-// order.  There is no split over keys: a window is a few hundred keys and the batch supplies the CTAs.
+// keys per copy instruction.  The copies are asynchronous into a per-warp ring in shared memory (each lane owns its
+// slots, so no barrier is needed), the pages of the window are looked up once per CTA, and so are the heads' distance
+// terms.  The lane's slice of q stays in registers for every head of the group; a score is a dot over the slice plus
+// log2(LPK) shuffles; the weighted values accumulate per lane and are summed over key groups and warps at the end, in
+// a fixed order.  There is no split over keys: a window is a few hundred keys and the batch supplies the CTAs.
 constexpr int WD_WARPS = 8;
-constexpr int WD_UNROLL = 4;
+constexpr int WD_UNROLL = 2;                      // key groups per ring stage
+constexpr int WD_STAGES = 4;
+constexpr size_t WD_RING_BYTES = static_cast<size_t>(WD_WARPS) * WD_STAGES * WD_UNROLL * 2 * 32 * 16;
 
 template <typename T> struct WdVec;
 template <> struct WdVec<__nv_bfloat16> {
@@ -220,7 +222,9 @@ window_sigmoid_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__
                                   int page, int window, float scale, int use_tab) {
   constexpr int VEC = WdVec<T>::N;
   constexpr int KPI = 32 / LPK;                      // keys per warp load
-  extern __shared__ __align__(16) float red[];       // [WD_WARPS][rep][dv]
+  extern __shared__ __align__(16) unsigned char wd_smem[];
+  uint4* ring = reinterpret_cast<uint4*>(wd_smem);   // [WD_WARPS][WD_STAGES][WD_UNROLL][K | V][32 lanes]
+  float* red = reinterpret_cast<float*>(wd_smem + WD_RING_BYTES);                          // [WD_WARPS][rep][dv]
   const int b = blockIdx.z, g = blockIdx.y;
   const int len = seq_len[b];
   const int rep = H / G;
@@ -262,27 +266,44 @@ window_sigmoid_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__
     }
   const float scale2 = scale * LOG2E;
   __syncthreads();
-  for (int base = j_lo + warp * KPI * WD_UNROLL; base <= p; base += WD_WARPS * KPI * WD_UNROLL) {
-    uint4 kr[WD_UNROLL], vr[WD_UNROLL];
+  // Each lane copies its own 16-byte slices of K and V asynchronously into its own slots of the warp's ring and reads
+  // them back itself, so the ring needs no barrier: WD_STAGES - 1 stages are in flight while one is multiplied.
+  uint4* myring = ring + static_cast<size_t>(warp) * WD_STAGES * WD_UNROLL * 2 * 32 + lane;
+  const int step = WD_WARPS * KPI * WD_UNROLL;
+  const int base0 = j_lo + warp * KPI * WD_UNROLL;
+  const int n_it = base0 <= p ? (p - base0) / step + 1 : 0;
+  auto issue = [&](int it) {
+    uint4* st = myring + (it % WD_STAGES) * WD_UNROLL * 2 * 32;
 #pragma unroll
     for (int u = 0; u < WD_UNROLL; ++u) {
-      const int j = base + u * KPI + grp;
-      kr[u] = make_uint4(0, 0, 0, 0);
-      vr[u] = make_uint4(0, 0, 0, 0);
-      if (j <= p) {
+      const int j = base0 + it * step + u * KPI + grp;
+      const bool ok = j <= p;
+      size_t slot = 0;
+      if (ok) {
         const int pg = j / page;
-        const size_t slot = static_cast<size_t>(pages[pg - pg0]) * page + (j - pg * page);
-        if (has_k) kr[u] = ldg_v4(k_cache + slot * G * d + g * d + c0);
-        if (has_v) vr[u] = ldg_v4(v_cache + slot * G * dv + g * dv + c0);
+        slot = static_cast<size_t>(pages[pg - pg0]) * page + (j - pg * page);
       }
+      cp_async_16(st + (u * 2) * 32, k_cache + slot * G * d + g * d + (has_k ? c0 : 0), ok && has_k);
+      cp_async_16(st + (u * 2 + 1) * 32, v_cache + slot * G * dv + g * dv + (has_v ? c0 : 0), ok && has_v);
     }
+  };
+#pragma unroll
+  for (int s0 = 0; s0 < WD_STAGES - 1; ++s0) {
+    if (s0 < n_it) issue(s0);
+    cp_async_commit();
+  }
+  for (int it = 0; it < n_it; ++it) {
+    cp_async_wait<WD_STAGES - 2>();                  // this thread's copies of stage `it` have landed
+    if (it + WD_STAGES - 1 < n_it) issue(it + WD_STAGES - 1);
+    cp_async_commit();
+    const uint4* st = myring + (it % WD_STAGES) * WD_UNROLL * 2 * 32;
 #pragma unroll
     for (int u = 0; u < WD_UNROLL; ++u) {
-      const int j = base + u * KPI + grp;
+      const int j = base0 + it * step + u * KPI + grp;
       const float dist = static_cast<float>(p - j);
       float kf[VEC], vf[VEC];
-      WdVec<T>::cvt(kr[u], kf);
-      WdVec<T>::cvt(vr[u], vf);
+      WdVec<T>::cvt(st[(u * 2) * 32], kf);
+      WdVec<T>::cvt(st[(u * 2 + 1) * 32], vf);
 #pragma unroll
       for (int r = 0; r < REP; ++r) {
         float s = 0.f;
@@ -304,6 +325,7 @@ window_sigmoid_attn_decode_kernel(const T* __restrict__ q, const T* __restrict__
       }
     }
   }
+  cp_async_wait<0>();
   // over the key groups of the warp, then over the warps
 #pragma unroll
   for (int r = 0; r < REP; ++r)
@@ -572,7 +594,7 @@ extern "C" int b2tts_window_sigmoid_attn(const void* q, const void* k_cache, con
     const int lpk = (widest + vec - 1) / vec;
     const size_t tab_bytes = sizeof(float) * rep * window;
     const int use_tab = tab_bytes <= 64 * 1024;          // larger windows compute the distance term per key
-    const size_t smem_d = sizeof(float) * WD_WARPS * rep * vdim + sizeof(int32_t) * ((window + page - 1) / page + 2) +
+    const size_t smem_d = WD_RING_BYTES + sizeof(float) * WD_WARPS * rep * vdim + sizeof(int32_t) * ((window + page - 1) / page + 2) +
                           (use_tab ? tab_bytes : 0);
     const dim3 grid_d(1, kv_heads, n_seqs);
     if (dtype == B2TTS_DTYPE_BF16)

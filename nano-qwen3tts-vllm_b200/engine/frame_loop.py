@@ -21,6 +21,7 @@ from .. import _native as nat
 from ..layers.linear import linear
 from ..sampling_params import SamplingParams
 from ..utils.context import reset_context, set_context
+from ..utils.graph_capture import graph_capture
 
 BF16 = torch.bfloat16
 
@@ -264,7 +265,7 @@ class DeviceFrameLoop:
         for t, v in zip(self._state(), state):               # the captured pass must also see a valid state
             t.copy_(v)
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        with graph_capture(self.graph):
             self._frame()
         torch.cuda.synchronize()
         for t, v in zip(self._state(), state):

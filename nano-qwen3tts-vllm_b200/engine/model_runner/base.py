@@ -22,6 +22,7 @@ from ...config import Config
 from ...layers.sampler import Sampler
 from ...utils.context import reset_context, set_context
 from ..sequence import Sequence
+from ...utils.graph_capture import graph_capture
 
 BF16 = torch.bfloat16
 
@@ -327,7 +328,7 @@ class ModelRunner:
             g = torch.cuda.CUDAGraph()
             self.set_decode_context(bs)
             self.decode_body(bs)                                             # warm-up at this size
-            with torch.cuda.graph(g, self.graph_pool):
+            with graph_capture(g, self.graph_pool):
                 self.graph_out[bs] = self.decode_body(bs)
             if self.graph_pool is None:
                 self.graph_pool = g.pool()

@@ -7,9 +7,10 @@ Differences from the embedding-driven runners of this package, all behind the sa
   * K and V pages are allocated per layer ([pages, page, kv_heads * dim] and [pages, page, kv_heads * vdim]), since a
     layer lists its own head counts and sizes;
   * activations and caches are bfloat16, or float32 when the engine is built with ``dtype="float32"`` (matrix
-    products then run as true 32-bit library GEMMs; TF32 stays off)."""
+    products then run as true 32-bit library GEMMs: TF32 is switched off around this runner's calls only)."""
 from __future__ import annotations
 
+import contextlib
 import os
 
 import torch
@@ -21,6 +22,21 @@ from ...utils.context import reset_context, set_context
 from ..sequence import Sequence
 from ..step_layout import MixedStepLayout
 from .base import ModelRunner
+from ...utils.graph_capture import graph_capture
+
+
+class _Float32Matmul:
+    """No TF32 and "highest" float32 precision inside the block."""
+
+    def __enter__(self):
+        self.saved = (torch.backends.cuda.matmul.allow_tf32, torch.get_float32_matmul_precision())
+        torch.backends.cuda.matmul.allow_tf32 = False
+        torch.set_float32_matmul_precision("highest")
+
+    def __exit__(self, *exc):
+        torch.set_float32_matmul_precision(self.saved[1])
+        torch.backends.cuda.matmul.allow_tf32 = self.saved[0]
+        return False
 
 
 class LMModelRunner(ModelRunner):
@@ -51,10 +67,6 @@ class LMModelRunner(ModelRunner):
 
     # ------------------------------------------------------------------ init
     def post_init(self):
-        if self.param_dtype == torch.float32:
-            torch.backends.cuda.matmul.allow_tf32 = False
-            torch.backends.cudnn.allow_tf32 = False
-            torch.set_float32_matmul_precision("highest")
         self.sampler = Sampler()
         self.top_k = 50
         self.max_step_tokens = self.config.max_num_batched_tokens
@@ -87,10 +99,16 @@ class LMModelRunner(ModelRunner):
             self.conv_state.append(st)
 
     # ------------------------------------------------------------------ the step
+    def true_float32(self):
+        """float32 mode: library matrix products in true 32-bit while this runner's code runs (the process-wide setting
+        is put back afterwards, so other models in the process keep theirs)."""
+        return _Float32Matmul() if self.param_dtype == torch.float32 else contextlib.nullcontext()
+
     def step_body(self) -> torch.Tensor:
         lay = self.layout
         set_context(False, step_layout=lay)
-        return self.model(lay.tokens, lay.positions)
+        with self.true_float32():
+            return self.model(lay.tokens, lay.positions)
 
     @torch.inference_mode()
     def capture_cudagraph(self):
@@ -103,7 +121,7 @@ class LMModelRunner(ModelRunner):
             self.step_body()                                                     # warm-up (weight packing, lazy handles)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, self.graph_pool):
+            with graph_capture(g, self.graph_pool):
                 self.graph_out[bs] = self.step_body()
             if self.graph_pool is None:
                 self.graph_pool = g.pool()
@@ -128,7 +146,8 @@ class LMModelRunner(ModelRunner):
         if not want_rows:
             return torch.empty(0, self.stack_config.vocab, dtype=torch.float32, device=self.device)
         rows = self.layout._view(self.layout.dev, "want_rows")[:len(want_rows)]
-        return self.model.compute_logits(x, rows)
+        with self.true_float32():
+            return self.model.compute_logits(x, rows)
 
     @torch.inference_mode()
     def sample(self, logits: torch.Tensor, temperatures: list[float], top_k: int) -> torch.Tensor:

@@ -12,6 +12,7 @@ from ...models.qwen3_tts_predictor import Qwen3TTSCodePredictorForCausalLM
 from ...utils.context import reset_context, set_context
 from ..sequence import PredictorSequence, Sequence  # noqa: F401  (re-exported like the reference)
 from .base import ModelRunner
+from ...utils.graph_capture import graph_capture
 
 
 class PredictorModelRunner(ModelRunner):
@@ -113,7 +114,7 @@ class PredictorModelRunner(ModelRunner):
             self.burst_body(bs)                                             # warm-up (packs lm_head images, lazy handles)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, self.graph_pool):
+            with graph_capture(g, self.graph_pool):
                 self.burst_body(bs)
             self.burst_graphs[bs] = g
         torch.cuda.synchronize()

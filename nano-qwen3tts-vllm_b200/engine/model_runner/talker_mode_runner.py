@@ -12,6 +12,7 @@ from ...models.qwen3_tts_talker import Qwen3TTSTalkerForCausalLM
 from ...utils.context import reset_context
 from ..sequence import Sequence
 from .base import BF16, ModelRunner
+from ...utils.graph_capture import graph_capture
 
 
 class TalkerModeModelRunner(ModelRunner):
@@ -87,7 +88,7 @@ class TalkerModeModelRunner(ModelRunner):
             body = lambda: self.model(st["embeds"][:t], st["index"][:t])
             body()                                                           # warm-up at this length (outside capture)
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, self.graph_pool):
+            with graph_capture(g, self.graph_pool):
                 ent["out"] = body()
             ent["graph"] = g
         ent["graph"].replay()

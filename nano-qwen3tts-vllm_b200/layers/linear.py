@@ -150,6 +150,15 @@ def linear_silu_mul(x: torch.Tensor, gate_up_weight: torch.Tensor, rounding: int
     return nat.silu_and_mul(gu[:, :n // 2], gu[:, n // 2:], rounding)
 
 
+def linear_relu_sq(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """max(x W^T, 0)^2 - the up projection of a squared-ReLU feed-forward with the activation in the GEMM epilogue on
+    the native path; the library GEMM followed by the in-place activation kernel elsewhere (long prompts, float32)."""
+    m, n = x.shape[0], weight.shape[0]
+    if x.dtype == torch.bfloat16 and native_ok(m, n, x.shape[1]):
+        return nat.gemm_bf16(x, packed_weight(weight), n, epilogue=nat.GEMM_RELU_SQ, pdl=PDL)
+    return nat.relu_sq_(linear(x, weight))
+
+
 class LinearBase(nn.Module):
     def __init__(self, input_size: int, output_size: int, bias: bool = False, tp_dim: int | None = None):
         super().__init__()

@@ -21,11 +21,10 @@ from torch import nn
 
 from .. import _native as nat
 from ..config import BokenexConfig, LayerSpec
-from ..layers.activation import ReluSquared
 from ..layers.attention import WindowSigmoidAttention
 from ..layers.embed_head import TokenPositionEmbedding
 from ..layers.layernorm import GainRMSNorm
-from ..layers.linear import MergedColumnParallelLinear, RowParallelLinear, ColumnParallelLinear, linear
+from ..layers.linear import MergedColumnParallelLinear, RowParallelLinear, ColumnParallelLinear, linear, linear_relu_sq
 from ..layers.moe import SigmoidTopKMoE
 from ..layers.short_conv import ShortConvQKV
 
@@ -50,10 +49,9 @@ class BokenexDenseFF(nn.Module):
         super().__init__()
         self.up = ColumnParallelLinear(width, ff)
         self.down = RowParallelLinear(ff, width)
-        self.act = ReluSquared()
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return self.down(self.act(self.up(h)))
+        return self.down(linear_relu_sq(h, self.up.weight))
 
 
 class BokenexLayer(nn.Module):

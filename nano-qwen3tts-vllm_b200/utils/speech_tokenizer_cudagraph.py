@@ -20,6 +20,7 @@ from typing import List, Tuple
 import torch
 
 from .. import _native as nat
+from .graph_capture import graph_capture
 
 
 class DecoderGraphs:
@@ -38,7 +39,7 @@ class DecoderGraphs:
                 self.eager(buf)
                 torch.cuda.synchronize(self.device)
                 g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, pool):
+                with graph_capture(g, pool):
                     out = self.eager(buf)
                 pool = pool or g.pool()
                 self.graphs[t], self.inputs[t], self.outputs[t] = g, buf, out

@@ -223,6 +223,20 @@ def test_bfloat16_window_edge_key_dominates(nat, window, page):
                 assert rel(out, ref) < 1e-2
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (37, 256, 192), (600, 128, 64)])
+def test_up_projection_with_squared_relu_epilogue(nat, m, n, k):
+    """The feed-forward's first half, max(x W^T, 0)^2: activation in the GEMM epilogue for decode-sized batches, library
+    GEMM + activation kernel for long portions; both against the plain model on the same bfloat16 inputs."""
+    from nano_qwen3tts_vllm_b200.layers.linear import linear_relu_sq
+    g = torch.Generator().manual_seed(m)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) * k ** -0.5).to(torch.bfloat16)
+    got = linear_relu_sq(x.to(DEV), w.to(DEV))
+    ref = O.relu_squared(x.double() @ w.double().T)
+    assert got.dtype == torch.bfloat16 and rel(got, ref) < 2e-2
+    assert (got.float() >= 0).all()
+
+
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 1e-2)])
 def test_far_key_among_hundreds(nat, dtype, tol):
     """A dominating key 699 or 700 positions back, behind hundreds of ordinary keys and a dozen page borders, with a
