@@ -539,6 +539,176 @@ static cudaError_t launch_window_mma(int max_new, int n_seqs, cudaStream_t st, c
   return cudaSuccess;
 }
 
+// ------------------------------------------------------------------ one new token per sequence on the tensor cores (bf16)
+// The rows of the m16n8k16 tile are the query HEADS of one key/value group (rep <= 16, the rest zero), so one pass over
+// K and V serves the whole group with a handful of instructions per key: S = Q K^T for 16 keys is D / 8 MMAs, the
+// weights are computed once per (head, key) from the float scores and the per-CTA distance table, and O += P V takes
+// D / 4 MMAs with the weights as a bf16 pair hi + lo.  One CTA per (sequence, key/value head), 4 warps; warp w owns the
+// 16-key tiles w, w + 4, ... of the window and streams them through its own two-stage ring of 16-byte asynchronous
+// copies (no CTA barrier in the loop); the warps' partial outputs are added in a fixed order at the end.
+constexpr int WT_WARPS = 4, WT_KEYS = 16;
+
+template <int D>
+__global__ void __launch_bounds__(WT_WARPS * 32)
+window_sigmoid_attn_decode_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                                      const __nv_bfloat16* __restrict__ v_cache, __nv_bfloat16* __restrict__ out,
+                                      const int32_t* __restrict__ seq_start, const int32_t* __restrict__ seq_pos0,
+                                      const int32_t* __restrict__ seq_len, const int32_t* __restrict__ block_tables, int bt_stride,
+                                      const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ pb,
+                                      int H, int G, int page, int window, float scale) {
+  constexpr int RS = D + 8, CH = D / 8;
+  constexpr float LOG2E = 1.4426950408889634f;
+  extern __shared__ __align__(16) unsigned char wt_smem[];
+  const int b = blockIdx.z, g = blockIdx.y;
+  const int len = seq_len[b];
+  const int rep = H / G;
+  const int n = seq_start[b];
+  if (len <= 0) {                                    // padding row of a captured step: defined output
+    for (int c = threadIdx.x; c < rep * D; c += blockDim.x) out[static_cast<size_t>(n) * H * D + g * rep * D + c] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  if (len != 1) return;
+  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(wt_smem);    // [WARPS][2 stages][K | V][KEYS][RS]
+  __nv_bfloat16* Qs = ring + WT_WARPS * 2 * 2 * WT_KEYS * RS;         // [16][RS]
+  float* red = reinterpret_cast<float*>(Qs + 16 * RS);                // [WARPS][rep][D]
+  int32_t* pages = reinterpret_cast<int32_t*>(red + WT_WARPS * rep * D);
+  float* tab = reinterpret_cast<float*>(pages + (window + page - 1) / page + 2);   // [rep][span]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int p = seq_pos0[b];
+  const int j_lo = max(0, p - window + 1), span = p - j_lo + 1;
+  const int32_t* bt = block_tables + static_cast<size_t>(b) * bt_stride;
+  for (int idx = tid; idx < 16 * CH; idx += blockDim.x) {
+    const int r = idx / CH, ch = idx % CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < rep) v = ldg_v4(q + static_cast<size_t>(n) * H * D + (g * rep + r) * D + ch * 8);
+    *reinterpret_cast<uint4*>(Qs + r * RS + ch * 8) = v;
+  }
+  const int pg0 = j_lo / page;
+  for (int i = tid; i <= p / page - pg0; i += blockDim.x) pages[i] = bt[pg0 + i];
+  for (int i = tid; i < rep * span; i += blockDim.x) {
+    const int r = i / span, h = g * rep + r;
+    tab[i] = LOG2E * (r1[h] * log1pf(r2[h] * static_cast<float>(i - r * span)) - pb[h]);
+  }
+  const float scale2 = scale * LOG2E;
+  __syncthreads();
+  uint32_t qa[D / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks)
+    ldsm_x4(qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], Qs + (lane & 15) * RS + ks * 16 + (lane >> 4) * 8);
+  float oacc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) oacc[i][e] = 0.f;
+  __nv_bfloat16* myring = ring + warp * 2 * 2 * WT_KEYS * RS;
+  const int n_tiles = (span + WT_KEYS - 1) / WT_KEYS;
+  const int n_my = warp < n_tiles ? (n_tiles - 1 - warp) / WT_WARPS + 1 : 0;
+  auto issue = [&](int i) {
+    const int j0 = j_lo + (warp + i * WT_WARPS) * WT_KEYS;
+    __nv_bfloat16* kd = myring + (i & 1) * 2 * WT_KEYS * RS;
+    __nv_bfloat16* vd = kd + WT_KEYS * RS;
+    const int jk = j0 + (lane & 15);                 // lanes 0..15 (and their mirrors) look one key's slot up each
+    int slot_k = 0;
+    if (jk <= p) {
+      const int pg = jk / page;
+      slot_k = pages[pg - pg0] * page + (jk - pg * page);
+    }
+#pragma unroll
+    for (int c = lane; c < WT_KEYS * CH; c += 32) {
+      const int key = c / CH, ch = c % CH;
+      const size_t slot = static_cast<size_t>(__shfl_sync(0xffffffffu, slot_k, key));
+      const bool ok = j0 + key <= p;
+      cp_async_16(kd + key * RS + ch * 8, k_cache + (slot * G + g) * D + ch * 8, ok);
+      cp_async_16(vd + key * RS + ch * 8, v_cache + (slot * G + g) * D + ch * 8, ok);
+    }
+  };
+  if (n_my > 0) issue(0);
+  cp_async_commit();
+  for (int i = 0; i < n_my; ++i) {
+    if (i + 1 < n_my) issue(i + 1);
+    cp_async_commit();
+    cp_async_wait<1>();                              // this lane's copies of tile i have landed ...
+    __syncwarp();                                    // ... and so have the other lanes'
+    const int j0 = j_lo + (warp + i * WT_WARPS) * WT_KEYS;
+    const __nv_bfloat16* Kt = myring + (i & 1) * 2 * WT_KEYS * RS;
+    const __nv_bfloat16* Vt = Kt + WT_KEYS * RS;
+    float sacc[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) sacc[nt][e] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4(b0, b1, b2, b3, Kt + ((lane >> 4) * 8 + (lane & 7)) * RS + ks * 16 + ((lane >> 3) & 1) * 8);
+      mma_bf16_16816(sacc[0], qa[ks], b0, b1);
+      mma_bf16_16816(sacc[1], qa[ks], b2, b3);
+    }
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int row = (lane >> 2) + (e >= 2 ? 8 : 0);
+        const int j = j0 + nt * 8 + 2 * (lane & 3) + (e & 1);
+        float w = 0.f;
+        if (row < rep && j <= p) w = __fdividef(1.0f, 1.0f + exp2f(tab[row * span + (p - j)] - sacc[nt][e] * scale2));
+        sacc[nt][e] = w;
+      }
+    uint32_t ah[4], al[4];
+    split_bf16(sacc[0][0], sacc[0][1], ah[0], al[0]);
+    split_bf16(sacc[0][2], sacc[0][3], ah[1], al[1]);
+    split_bf16(sacc[1][0], sacc[1][1], ah[2], al[2]);
+    split_bf16(sacc[1][2], sacc[1][3], ah[3], al[3]);
+#pragma unroll
+    for (int np = 0; np < D / 16; ++np) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4_t(b0, b1, b2, b3, Vt + (((lane >> 3) & 1) * 8 + (lane & 7)) * RS + np * 16 + (lane >> 4) * 8);
+      mma_bf16_16816(oacc[2 * np], ah, b0, b1);
+      mma_bf16_16816(oacc[2 * np], al, b0, b1);
+      mma_bf16_16816(oacc[2 * np + 1], ah, b2, b3);
+      mma_bf16_16816(oacc[2 * np + 1], al, b2, b3);
+    }
+    __syncwarp();                                    // every lane is done with this stage before it is refilled
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int nt = 0; nt < D / 8; ++nt) {
+    const int col = nt * 8 + 2 * (lane & 3);
+    const int ra = lane >> 2, rb = ra + 8;
+    if (ra < rep) { red[(warp * rep + ra) * D + col] = oacc[nt][0]; red[(warp * rep + ra) * D + col + 1] = oacc[nt][1]; }
+    if (rb < rep) { red[(warp * rep + rb) * D + col] = oacc[nt][2]; red[(warp * rep + rb) * D + col + 1] = oacc[nt][3]; }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < rep * D; idx += blockDim.x) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < WT_WARPS; ++w) t += red[w * rep * D + idx];
+    out[static_cast<size_t>(n) * H * D + g * rep * D + idx] = __float2bfloat16_rn(t);
+  }
+}
+
+template <int D>
+static size_t window_decode_mma_smem(int rep, int page, int window) {
+  return sizeof(__nv_bfloat16) * (WT_WARPS * 2 * 2 * WT_KEYS + 16) * (D + 8) + sizeof(float) * WT_WARPS * rep * D +
+         sizeof(int32_t) * ((window + page - 1) / page + 2) + sizeof(float) * rep * window;
+}
+
+template <int D>
+static cudaError_t launch_window_decode_mma(int n_seqs, cudaStream_t st, const void* q, const void* kc, const void* vc, void* out,
+                                            const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len,
+                                            const int32_t* bt, int bt_stride, const float* r1, const float* r2, const float* pb, int H,
+                                            int G, int page, int window, float scale) {
+  auto kern = window_sigmoid_attn_decode_mma_kernel<D>;
+  const size_t smem = window_decode_mma_smem<D>(H / G, page, window);
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  if (e != cudaSuccess) return e;
+  using B = __nv_bfloat16;
+  kern<<<dim3(1, G, n_seqs), WT_WARPS * 32, smem, st>>>(static_cast<const B*>(q), static_cast<const B*>(kc), static_cast<const B*>(vc),
+                                                        static_cast<B*>(out), seq_start, seq_pos0, seq_len, bt, bt_stride, r1, r2, pb,
+                                                        H, G, page, window, scale);
+  return cudaSuccess;
+}
+
 template <typename T, int LPK>
 static cudaError_t launch_window_decode_rep(int rep, dim3 grid, size_t smem, cudaStream_t st, const void* q, const void* kc, const void* vc,
                                             void* out, const int32_t* seq_start, const int32_t* seq_pos0, const int32_t* seq_len,
@@ -590,7 +760,21 @@ extern "C" int b2tts_window_sigmoid_attn(const void* q, const void* k_cache, con
   const int widest = dim > vdim ? dim : vdim;
   const bool stream_ok = dim % vec == 0 && vdim % vec == 0 && widest <= 32 * vec && rep <= 8 && aligned16(q) && aligned16(k_cache) &&
                          aligned16(v_cache);
-  if (stream_ok) {
+  const bool tensor_shape = stream_ok && dtype == B2TTS_DTYPE_BF16 && dim == vdim && (dim == 32 || dim == 64 || dim == 96 || dim == 128);
+  size_t smem_t = 0;
+  if (tensor_shape && rep <= 16)
+    smem_t = dim == 32 ? window_decode_mma_smem<32>(rep, page, window) : dim == 64 ? window_decode_mma_smem<64>(rep, page, window)
+           : dim == 96 ? window_decode_mma_smem<96>(rep, page, window) : window_decode_mma_smem<128>(rep, page, window);
+  const bool decode_tensor = smem_t > 0 && smem_t <= 200 * 1024;
+  if (decode_tensor) {
+#define WT_GO(DD) e = launch_window_decode_mma<DD>(n_seqs, st, q, k_cache, v_cache, out, seq_start, seq_pos0, seq_len, block_tables, \
+                                                   bt_stride, r1, r2, pb, heads, kv_heads, page, window, scale)
+    if (dim == 32) WT_GO(32); else if (dim == 64) WT_GO(64); else if (dim == 96) WT_GO(96); else WT_GO(128);
+#undef WT_GO
+    if (e != cudaSuccess) return cuda_fail(e, "window_sigmoid_attn (one token, tensor)");
+    B2_CHECK_LAUNCH("window_sigmoid_attn (one token, tensor)");
+    if (max_new == 1) return B2TTS_OK;
+  } else if (stream_ok) {
     const int lpk = (widest + vec - 1) / vec;
     const size_t tab_bytes = sizeof(float) * rep * window;
     const int use_tab = tab_bytes <= 64 * 1024;          // larger windows compute the distance term per key
