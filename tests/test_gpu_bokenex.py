@@ -457,6 +457,30 @@ def test_bfloat16_serving_precision_and_cut_independence():
         assert e.median().item() < 0.03 and (e > 0.1).float().mean().item() < 0.1, e
 
 
+def test_bfloat16_wide_group_mixed_batch_equals_each_alone():
+    """Six query heads on one key/value head of 64, window shorter than the prompts, bfloat16 with CUDA graphs: a batch
+    that mixes portions and decoded tokens of three requests over reused pages and slots gives each request the
+    logits it gets alone (rounding apart) and stays close to the plain model."""
+    cfg = O.random_config(6, width=128, heads=12, kv_heads=2, dim=64, vdim=64, ff=128, expert_ff=64, window=37, taps=4,
+                          kinds=("dense", "moe"), n_layers=2, vocab=96, max_positions=160)
+    sd = O.random_weights(cfg, seed=12)
+    req = {"a": tokens_for(cfg, 120, 1), "b": tokens_for(cfg, 75, 2), "c": tokens_for(cfg, 60, 3)}
+    ref = {i: O.forward(cfg, sd, t) for i, t in req.items()}
+    eng = make_engine(cfg, sd, dtype="bfloat16", eager=False, pages=5, page=64, seqs=2, slots=2)
+    try:
+        alone = {i: replay(eng, {i: t}, [[(i, len(t) - 20)]] + [[(i, 1)]] * 20)[i] for i, t in req.items()}
+        sched = [[("a", 70)], [("a", 30), ("b", 40)]] + [[("a", 1), ("b", 7)]] * 5 + [[("a", 1)]] * 15     # a ends: 120
+        sched += [[("c", 33)], [("c", 2)]] + [[("c", 1)]] * 25                                              # c reuses a's pages
+        mixed = replay(eng, {"a": req["a"], "b": req["b"], "c": req["c"]}, sched)
+        assert len(eng.scheduler.block_manager.free_block_ids) == 5 and eng.scheduler.state_slots.available() == 2
+    finally:
+        eng.exit()
+    for i in req:
+        for got, want in ((alone[i], ref[i]), (mixed[i], ref[i]), (mixed[i], alone[i])):
+            e = nerr_rows(got, want)
+            assert e.median().item() < 0.03 and (e > 0.1).float().mean().item() < 0.1, (i, e)
+
+
 def test_greedy_generation_through_the_scheduler():
     """``generate`` with top_k = 1: prompts of unequal length, a token budget that cuts the prompts into portions, fewer
     state slots than requests (the rest wait).  Every generated token must be the plain model's argmax, or lie within
