@@ -259,10 +259,17 @@ conv_headnorm_kvwrite_vec4_kernel(const T* __restrict__ u, int64_t u_stride, con
       for (int j = 0; j < TAPS; ++j) w[i][e][j] = 0.f;
     }
     if (cc < width) {
+      // the lane's 4 channels x TAPS taps are 16 * TAPS contiguous, 16-byte aligned bytes: TAPS vector loads
+      float flat[4 * TAPS];
+#pragma unroll
+      for (int v = 0; v < TAPS; ++v) {
+        const float4 r = *reinterpret_cast<const float4*>(conv_w + static_cast<size_t>(c0 + cc) * TAPS + 4 * v);
+        flat[4 * v] = r.x; flat[4 * v + 1] = r.y; flat[4 * v + 2] = r.z; flat[4 * v + 3] = r.w;
+      }
 #pragma unroll
       for (int e = 0; e < 4; ++e)
 #pragma unroll
-        for (int j = 0; j < TAPS; ++j) w[i][e][j] = conv_w[static_cast<size_t>(c0 + cc + e) * TAPS + j];
+        for (int j = 0; j < TAPS; ++j) w[i][e][j] = flat[e * TAPS + j];
       if (kind != 2) {
         const float4 r = *reinterpret_cast<const float4*>((kind == 0 ? q_norm_w : k_norm_w) + cc);
         g4[i][0] = r.x; g4[i][1] = r.y; g4[i][2] = r.z; g4[i][3] = r.w;
