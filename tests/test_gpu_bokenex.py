@@ -457,6 +457,29 @@ def test_bfloat16_serving_precision_and_cut_independence():
         assert e.median().item() < 0.03 and (e > 0.1).float().mean().item() < 0.1, e
 
 
+@pytest.mark.parametrize("dtype,tol", [("float32", 2e-5), ("bfloat16", None)])
+def test_sizes_that_fit_no_vector_width(dtype, tol):
+    """Width, head sizes, inner sizes and vocabulary that are multiples of 2 only (no 16-byte rows anywhere), five heads
+    that each own their key/value head, two taps, one expert of three: every kernel takes its general path."""
+    cfg = O.random_config(7, width=50, vocab=41, heads=5, kv_heads=5, dim=6, vdim=10, ff=42, expert_ff=22, experts=3, top=1,
+                          taps=2, window=13, kinds=("moe", "dense", None), n_layers=3, max_positions=80)
+    sd = O.random_weights(cfg, seed=4)
+    toks = tokens_for(cfg, 70, 5)
+    ref = O.forward(cfg, sd, toks)
+    eng = make_engine(cfg, sd, dtype=dtype, pages=3, page=64, seqs=2)
+    try:
+        whole = replay(eng, {"a": toks}, [[("a", 70)]])["a"]
+        cut = replay(eng, {"b": toks}, [[("b", 31)], [("b", 2)], [("b", 17)]] + [[("b", 1)]] * 20)["b"]
+    finally:
+        eng.exit()
+    if tol is not None:
+        assert nerr(whole, ref) < tol and nerr(cut, ref) < tol
+    else:
+        for got, want in ((whole, ref), (cut, ref), (cut, whole)):
+            e = nerr_rows(got, want)
+            assert e.median().item() < 0.03 and (e > 0.1).float().mean().item() < 0.1, e
+
+
 def test_bfloat16_wide_group_mixed_batch_equals_each_alone():
     """Six query heads on one key/value head of 64, window shorter than the prompts, bfloat16 with CUDA graphs: a batch
     that mixes portions and decoded tokens of three requests over reused pages and slots gives each request the
