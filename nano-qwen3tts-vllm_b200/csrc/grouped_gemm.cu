@@ -98,18 +98,21 @@ grouped_gemm_kernel(const T* __restrict__ A, int64_t lda, const T* __restrict__ 
 }
 
 // ------------------------------------------------------------------ bf16 on the tensor cores
-// 128 x 128 output tile per CTA, K walked in 32-wide slices through a four-stage ring of 16-byte asynchronous copies
+// 128 x 128 output tile per CTA, K walked in 64-wide slices through a three-stage ring of 16-byte asynchronous copies
 // (rows of A are gathered through `in_rows`; rows of W beyond N and slices beyond K arrive as zeros).  Shared rows are
-// padded to 80 bytes, which puts the eight rows of an ldmatrix phase into eight different 16-byte bank groups.  Eight
+// padded to 144 bytes, which puts the eight rows of an ldmatrix phase into eight different 16-byte bank groups.  Eight
 // warps as 2 (rows) x 4 (columns), a warp owns 64 x 32 as 4 x 4 m16n8k16 accumulators in float.  A 16-row block with
 // no row of the group is skipped by its warp, so a decode step (a handful of rows per expert) spends its time
 // streaming W once, not multiplying zeros; rows of A beyond the group are not even loaded, since an output row
 // depends on its own input row only and those outputs are never stored.
-// For decode-sized groups the same kernel runs with 32-row tiles (one row of eight warps, 32 x 16 each) and an eight-stage
-// ring: the A tile is small, so twice the bytes of W are in flight per SM.
-constexpr int GM_BN = 128, GM_BK = 32, GM_THREADS = 256, GM_LD = GM_BK + 8;
+// For decode-sized groups the same kernel runs with 32-row tiles (one row of eight warps, 32 x 16 each) and a four-stage
+// ring: the A tile is small, so more bytes of W are in flight per SM.
+constexpr int GM_BN = 128, GM_BK = 64, GM_THREADS = 256, GM_LD = GM_BK + 8;
+constexpr int GM_CPR = GM_BK / 8;                  // 16-byte chunks per tile row
+constexpr int GM_RPP = GM_THREADS / GM_CPR;        // tile rows one pass of the CTA's loader covers
+constexpr int GM_PASSES = 128 / GM_RPP;
 template <int BM> struct GmShape {
-  static constexpr int STAGES = BM == 128 ? 4 : 8;
+  static constexpr int STAGES = BM == 128 ? 3 : 4;
   static constexpr int WARPS_M = BM == 128 ? 2 : 1, WARPS_N = 8 / WARPS_M;
   static constexpr int MT = BM / WARPS_M / 16, NT = GM_BN / WARPS_N / 8;
   static constexpr size_t SMEM = sizeof(__nv_bfloat16) * STAGES * (BM + GM_BN) * GM_LD + sizeof(int) * 2 * BM;
@@ -153,21 +156,21 @@ grouped_gemm_mma_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const 
   }
   __syncthreads();
   const __nv_bfloat16* We = W + static_cast<size_t>(e) * N * K;
-  // loader: chunk id = tid + 256 * i -> row id / 4, 8 columns from (id % 4) * 8
-  int a_row[2], w_row[2];
+  // loader: pass i covers tile rows GM_RPP * i + tid / GM_CPR, 8 columns from (tid % GM_CPR) * 8
+  int a_row[GM_PASSES], w_row[GM_PASSES];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int r = (tid + GM_THREADS * i) >> 2;
+  for (int i = 0; i < GM_PASSES; ++i) {
+    const int r = GM_RPP * i + tid / GM_CPR;
     a_row[i] = r < GM_BM ? in_rows[r] : -1;
     w_row[i] = n0 + r < N ? n0 + r : -1;
   }
-  const int ck = (tid & 3) * 8;
+  const int ck = (tid % GM_CPR) * 8;
   const int nk = (K + GM_BK - 1) / GM_BK;
   auto load = [&](int stage, int kt) {
     const int k = kt * GM_BK + ck;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int r = (tid + GM_THREADS * i) >> 2;
+    for (int i = 0; i < GM_PASSES; ++i) {
+      const int r = GM_RPP * i + tid / GM_CPR;
       if (a_row[i] >= 0)
         cp_async_16(As + (stage * GM_BM + r) * GM_LD + ck, A + static_cast<int64_t>(a_row[i]) * lda + (k < K ? k : 0), k < K);
       const bool okw = w_row[i] >= 0 && k < K;
