@@ -455,18 +455,61 @@ B2TTS_API int b2tts_window_sigmoid_attn(const void* q, const void* k_cache, cons
                                         const int32_t* block_tables, int bt_stride, const float* r1, const float* r2,
                                         const float* pb, int n_seqs, int max_new, int heads, int kv_heads, int dim, int vdim,
                                         int page, int window, float scale, int dtype, void* stream);
-/* Sigmoid top-k router: scores = sigmoid(h router^T) in float; top_idx [n, top] the `top` largest (ties: lower index),
- * top_w = score / (sum of the chosen + 1e-20) * scale; then the (token, choice) pairs grouped by expert:
+/* Top-k router, in float.  softmax_chosen == 0: scores = sigmoid(h router^T), top_w = score / (sum of the chosen + 1e-20)
+ * * scale.  softmax_chosen == 1: scores = h router^T + bias (bias may be null), top_w = softmax over the chosen scores only,
+ * * scale.  top_idx [n, top] the `top` largest (ties: lower index); then the (token, choice) pairs grouped by expert:
  * offsets [experts + 1], sorted_pair [n * top] (pair = token * top + choice; order inside a group unspecified). */
 B2TTS_API int b2tts_moe_route(const void* h, const float* router, int32_t* top_idx, float* top_w, int32_t* offsets,
-                              int32_t* sorted_pair, int n_tokens, int cols, int experts, int top, float scale, int dtype,
-                              void* stream);
+                              int32_t* sorted_pair, int n_tokens, int cols, int experts, int top, float scale,
+                              const float* bias, int softmax_chosen, int dtype, void* stream);
 /* C[out_row(s), :] = act(A[in_row(s), :] W[e]^T) for s in offsets[e] .. offsets[e+1], W [experts, n, k];
  * in_row(s) = sorted_pair[s] / top if in_by_token else s; out_row(s) = sorted_pair[s] if out_by_pair else s;
  * act 0 = none, 1 = squared ReLU; float accumulation. */
 B2TTS_API int b2tts_grouped_gemm(const void* a, int64_t lda, const void* w, void* c, int64_t ldc, const int32_t* offsets,
                                  const int32_t* sorted_pair, int n_pairs, int experts, int n, int k, int top, int in_by_token,
                                  int out_by_pair, int act, int dtype, void* stream);
+
+/* ---- decoders with latent attention, token shift and a norm on each sublayer's output (csrc/latent_ops.cu, latent_attn.cu).
+ * `dtype` is the activation / cache type (B2TTS_DTYPE_*); x is the float residual stream [rows, cols]. */
+/* x[i] = embed[tokens[i]] * scale. */
+B2TTS_API int b2tts_embed_scale(const int32_t* tokens, const void* embed, float* x, int rows, int cols, int vocab, float scale,
+                                int dtype, void* stream);
+/* out[t] = x[t] + (prev - x[t]) * mu; prev = x[t-1] inside a sequence's portion, state[seq_slot] at its first token, zero at
+ * position 0; then state[seq_slot] = the sequence's last row of this step.  Rows of sequences with seq_len 0 give zeros. */
+B2TTS_API int b2tts_token_shift(const float* x, const float* mu, float* state, const int32_t* tok_seq, const int32_t* positions,
+                                const int32_t* seq_start, const int32_t* seq_len, const int32_t* seq_slot, void* out,
+                                int n_tokens, int cols, int dtype, void* stream);
+/* Row t of the merged projection u (row stride ldu): cq[t] = rms_norm(u[t, q_off : q_off + q_rank]) * q_norm_w (skipped when
+ * q_rank == 0); cache[slot_mapping[t]] = [rms_norm(u[t, kv_off : +kv_rank]) * kv_norm_w | rotate(u[t, kv_off + kv_rank : +rot_dim])],
+ * pair (2i, 2i+1), i < rot_dims / 2, turned by positions[t] * freq[i], cos and sin times rot_mult.  Slot -1: no cache write. */
+B2TTS_API int b2tts_latent_prep(const void* u, int64_t ldu, int q_off, int kv_off, void* cq, const float* q_norm_w,
+                                const float* kv_norm_w, const float* freq, float rot_mult, const int32_t* positions,
+                                const int32_t* slot_mapping, void* cache, int n_tokens, int q_rank, int kv_rank, int rot_dim,
+                                int rot_dims, float eps, int dtype, void* stream);
+/* Multi-query softmax attention over cached rows [c | kr] with a sink in the denominator; see csrc/latent_attn.cu.
+ * ql: absorbed queries (element (t, h, :) at ql + t * ql_tok + h * ql_head, kv_rank numbers), qr: rotary query parts, not yet
+ * turned (rot_dim numbers), out: weighted latent sums (kv_rank numbers), strides in elements.  window 0 = every earlier key.
+ * path 0 = choose, 1 = the plain kernel, 2 = the tensor-core kernel (bf16; fails if the sizes do not fit it). */
+B2TTS_API int b2tts_latent_attn(const void* ql, int64_t ql_tok, int64_t ql_head, const void* qr, int64_t qr_tok, int64_t qr_head,
+                                const void* cache, void* out, int64_t o_tok, int64_t o_head, const float* sink, const float* freq,
+                                float rot_mult, int rot_dims, const int32_t* seq_start, const int32_t* seq_pos0,
+                                const int32_t* seq_len, const int32_t* block_tables, int64_t bt_stride, int n_seqs, int max_new,
+                                int heads, int kv_rank, int rot_dim, int page, int window, float scale, int dtype, int path,
+                                void* stream);
+/* out[t, h * vdim + d] = v[t * v_tok + h * v_head + d] * sigmoid(gate[t * ldg + h * vdim + d]) (gate null: the copy alone). */
+B2TTS_API int b2tts_gate_heads(const void* v, int64_t v_tok, int64_t v_head, const void* gate, int64_t ldg, void* out, int n,
+                               int heads, int vdim, int dtype, void* stream);
+/* y = a + sum_k zw[:, k] z[:, k] (a or z may be null); x += w * y / sqrt(mean over the group (y^2) + eps), the row cut into
+ * `groups` equal consecutive parts; copy (optional) = the new x in the activation type. */
+B2TTS_API int b2tts_group_norm_residual(float* x, const void* a, const void* z, const float* zw, int top, const float* w, int groups,
+                                        float eps, void* copy, int rows, int cols, int dtype, void* stream);
+/* out[i] = group RMS norm of x[rows_idx[i]] times w (rows_idx null: row i; w null: the conversion alone). */
+B2TTS_API int b2tts_gather_group_norm(const float* x, const int32_t* rows_idx, void* out, const float* w, int groups, float eps,
+                                      int rows, int cols, int dtype, void* stream);
+/* In place: z = y + bias (bias [cols] or null); y = z > 0 ? softplus(pq[0]) z^2 + z/2 : (1/2 + softplus(pq[1])) (e^z - 1 - z) + z/2. */
+B2TTS_API int b2tts_xielu(void* y, const void* bias, const float* pq, int64_t rows, int cols, int dtype, void* stream);
+/* y[r, c] = silu(gu[r, c]) * gu[r, ff + c], gu [rows, 2 ff]. */
+B2TTS_API int b2tts_silu_mul(const void* gu, void* y, int64_t rows, int ff, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

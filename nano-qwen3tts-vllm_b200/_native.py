@@ -85,7 +85,16 @@ def _load():
         "b2tts_relu_sq": (I, [P, L, I, P]),
         "b2tts_conv_headnorm_kvwrite": (I, [P, L, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P]),
         "b2tts_window_sigmoid_attn": (I, [P, P, P, P, P, P, P, P, I, P, P, P, I, I, I, I, I, I, I, I, F, I, P]),
-        "b2tts_moe_route": (I, [P, P, P, P, P, P, I, I, I, I, F, I, P]),
+        "b2tts_moe_route": (I, [P, P, P, P, P, P, I, I, I, I, F, P, I, I, P]),
+        "b2tts_embed_scale": (I, [P, P, P, I, I, I, F, I, P]),
+        "b2tts_token_shift": (I, [P, P, P, P, P, P, P, P, P, I, I, I, P]),
+        "b2tts_latent_prep": (I, [P, L, I, I, P, P, P, P, F, P, P, P, I, I, I, I, I, F, I, P]),
+        "b2tts_latent_attn": (I, [P, L, L, P, L, L, P, P, L, L, P, P, F, I, P, P, P, P, L, I, I, I, I, I, I, I, F, I, I, P]),
+        "b2tts_gate_heads": (I, [P, L, L, P, L, P, I, I, I, I, P]),
+        "b2tts_group_norm_residual": (I, [P, P, P, P, I, P, I, F, P, I, I, I, P]),
+        "b2tts_gather_group_norm": (I, [P, P, P, P, I, F, I, I, I, P]),
+        "b2tts_xielu": (I, [P, P, P, L, I, I, P]),
+        "b2tts_silu_mul": (I, [P, P, L, I, I, P]),
         "b2tts_grouped_gemm": (I, [P, L, P, P, L, P, P, I, I, I, I, I, I, I, I, I, P]),
     }
     for name, (res, args) in sig.items():
@@ -754,12 +763,17 @@ def window_sigmoid_attn(q, k_cache, v_cache, out, lay, r1, r2, pb, heads, kv_hea
         scale, dt, _stream()), "window_sigmoid_attn")
 
 
-def moe_route(h, router, top_idx, top_w, offsets, sorted_pair, top, scale):
+def moe_route(h, router, top_idx, top_w, offsets, sorted_pair, top, scale, bias=None, softmax_chosen=False):
+    """``softmax_chosen``: scores are the logits (+ ``bias``) and the weights their softmax over the chosen ones;
+    otherwise sigmoid scores divided by the sum of the chosen."""
     dt = _act(h, "h")
     _cuda(router, F32, "router")
+    if bias is not None:
+        _cuda(bias, F32, "bias")
     n, cols = h.shape
     _check(_load().b2tts_moe_route(h.data_ptr(), router.data_ptr(), top_idx.data_ptr(), top_w.data_ptr(), offsets.data_ptr(),
-                                   sorted_pair.data_ptr(), n, cols, router.shape[0], top, scale, dt, _stream()), "moe_route")
+                                   sorted_pair.data_ptr(), n, cols, router.shape[0], top, scale, _ptr(bias), int(softmax_chosen),
+                                   dt, _stream()), "moe_route")
 
 
 def grouped_gemm(a, w, c, offsets, sorted_pair, n_pairs, top, in_by_token, out_by_pair, act):
@@ -770,3 +784,94 @@ def grouped_gemm(a, w, c, offsets, sorted_pair, n_pairs, top, in_by_token, out_b
     _check(_load().b2tts_grouped_gemm(a.data_ptr(), a.stride(0), w.data_ptr(), c.data_ptr(), c.stride(0), offsets.data_ptr(),
                                       sorted_pair.data_ptr(), n_pairs, e, n, k, top, int(in_by_token), int(out_by_pair), int(act),
                                       dt, _stream()), "grouped_gemm")
+
+
+# ------------------------------------------------------------------------------------------ latent-attention decoders
+def embed_scale(tokens, embed, scale, x):
+    """x [n, D] float <- embed[tokens] * scale."""
+    dt = _act(embed, "embed")
+    _cuda(tokens, I32, "tokens"); _cuda(x, F32, "x")
+    _check(_load().b2tts_embed_scale(tokens.data_ptr(), embed.data_ptr(), x.data_ptr(), x.shape[0], x.shape[1], embed.shape[0],
+                                     scale, dt, _stream()), "embed_scale")
+
+
+def token_shift(x, mu, state, lay, out):
+    """out [n, D] <- x + (previous row - x) * mu; ``state`` [slots, D] float carries a sequence's last row between steps."""
+    _cuda(x, F32, "x"); _cuda(mu, F32, "mu"); _cuda(state, F32, "state")
+    dt = _act(out, "out")
+    assert x.is_contiguous() and state.is_contiguous() and state.shape[1] == x.shape[1]
+    _check(_load().b2tts_token_shift(x.data_ptr(), mu.data_ptr(), state.data_ptr(), lay.tok_seq.data_ptr(), lay.positions.data_ptr(),
+                                     lay.seq_start.data_ptr(), lay.seq_len.data_ptr(), lay.seq_slot.data_ptr(), out.data_ptr(),
+                                     lay.n_tokens, x.shape[1], dt, _stream()), "token_shift")
+
+
+def latent_prep(u, q_off, kv_off, cq, q_norm_w, kv_norm_w, freq, rot_mult, lay, cache, q_rank, kv_rank, rot_dim, rot_dims, eps):
+    dt = _act(u, "u")
+    assert cache.dtype == u.dtype and cache.is_contiguous() and (cq is None or (cq.dtype == u.dtype and cq.is_contiguous()))
+    _check(_load().b2tts_latent_prep(u.data_ptr(), u.stride(0), q_off, kv_off, _ptr(cq), _ptr(q_norm_w), kv_norm_w.data_ptr(),
+                                     _ptr(freq), rot_mult, lay.positions.data_ptr(), lay.slot_mapping.data_ptr(), cache.data_ptr(),
+                                     lay.n_tokens, q_rank, kv_rank, rot_dim, rot_dims, eps, dt, _stream()), "latent_prep")
+
+
+LATENT_ATTN_AUTO, LATENT_ATTN_PLAIN, LATENT_ATTN_TENSOR = 0, 1, 2
+
+
+def latent_attn(ql, ql_strides, qr, qr_strides, cache, out, out_strides, sink, freq, rot_mult, rot_dims, lay, heads, kv_rank,
+                rot_dim, page, window, scale, path=LATENT_ATTN_AUTO):
+    """``ql`` / ``qr`` / ``out``: tensors whose element (token t, head h, :) lies at t * strides[0] + h * strides[1]."""
+    dt = _act(cache, "cache")
+    assert ql.dtype == cache.dtype and qr.dtype == cache.dtype and out.dtype == cache.dtype
+    _check(_load().b2tts_latent_attn(ql.data_ptr(), ql_strides[0], ql_strides[1], qr.data_ptr(), qr_strides[0], qr_strides[1],
+                                     cache.data_ptr(), out.data_ptr(), out_strides[0], out_strides[1], sink.data_ptr(), _ptr(freq),
+                                     rot_mult, rot_dims, lay.seq_start.data_ptr(), lay.seq_pos0.data_ptr(), lay.seq_len.data_ptr(),
+                                     lay.block_tables.data_ptr(), lay.block_tables.stride(0), lay.n_seqs, lay.max_new, heads,
+                                     kv_rank, rot_dim, page, window, scale, dt, path, _stream()), "latent_attn")
+
+
+def gate_heads(v, v_strides, gate, out, heads, vdim):
+    """out [n, heads * vdim] <- v (token / head strides given) * sigmoid(gate) (``gate``: a column slice, or None)."""
+    dt = _act(out, "out")
+    assert v.dtype == out.dtype and (gate is None or (gate.dtype == out.dtype and gate.stride(1) == 1))
+    _check(_load().b2tts_gate_heads(v.data_ptr(), v_strides[0], v_strides[1], _ptr(gate), 0 if gate is None else gate.stride(0),
+                                    out.data_ptr(), out.shape[0], heads, vdim, dt, _stream()), "gate_heads")
+
+
+def group_norm_residual(x, a, z, zw, w, groups, eps, copy, dtype):
+    """x += w * group_rms_norm(a + sum_k zw[:, k] z[:, k]); ``copy`` (optional) <- the new x in ``dtype``."""
+    _cuda(x, F32, "x"); _cuda(w, F32, "w")
+    n, cols = x.shape
+    top = 0 if z is None else zw.shape[1]
+    for t in (a, z, copy):
+        assert t is None or (t.dtype == dtype and t.is_contiguous())
+    _check(_load().b2tts_group_norm_residual(x.data_ptr(), _ptr(a), _ptr(z), _ptr(zw), top, w.data_ptr(), groups, eps, _ptr(copy),
+                                             n, cols, DTYPE_CODE[dtype], _stream()), "group_norm_residual")
+
+
+def gather_group_norm(x, rows, w, groups, eps, dtype, out=None):
+    """out[i] = group_rms_norm(x[rows[i]]) * w (``rows`` None: every row; ``w`` None: the type conversion alone)."""
+    _cuda(x, F32, "x")
+    n = x.shape[0] if rows is None else rows.shape[0]
+    if out is None:
+        out = torch.empty(n, x.shape[1], dtype=dtype, device=x.device)
+    _check(_load().b2tts_gather_group_norm(x.data_ptr(), _ptr(rows), out.data_ptr(), _ptr(w), groups, eps, n, x.shape[1],
+                                           DTYPE_CODE[dtype], _stream()), "gather_group_norm")
+    return out
+
+
+def xielu_(y, bias, pq):
+    """In place on y [rows, cols]: add ``bias`` (or None), then xIELU with the two raw parameters ``pq`` (float [2])."""
+    dt = _act(y, "y")
+    _cuda(pq, F32, "pq")
+    assert bias is None or bias.dtype == y.dtype
+    _check(_load().b2tts_xielu(y.data_ptr(), _ptr(bias), pq.data_ptr(), y.numel() // y.shape[-1], y.shape[-1], dt, _stream()), "xielu")
+    return y
+
+
+def silu_mul(gu, out=None):
+    """gu [rows, 2 ff] = [gate | up] -> silu(gate) * up."""
+    dt = _act(gu, "gu")
+    ff = gu.shape[1] // 2
+    if out is None:
+        out = torch.empty(gu.shape[0], ff, dtype=gu.dtype, device=gu.device)
+    _check(_load().b2tts_silu_mul(gu.data_ptr(), out.data_ptr(), gu.shape[0], ff, dt, _stream()), "silu_mul")
+    return out

@@ -121,6 +121,9 @@ class FeedForwardSpec:
     experts: int = 0
     top: int = 0
     router_scale: float = 1.0
+    act: str = "relu2"             # "relu2": relu(up)^2;  "xielu": two learned numbers;  "silu_gate": silu(gate) * up
+    bias: bool = False             # dense projections carry biases
+    router: str = "sigmoid"        # "sigmoid": scores / their sum;  "softmax_chosen": logits + bias, softmax over the chosen
 
 
 @dataclass
@@ -192,6 +195,131 @@ class BokenexConfig:
         return {"architecture": self.architecture, "vocab": self.vocab, "width": self.width,
                 "max_positions": self.max_positions, "norm": {"eps": self.norm_eps},
                 "residual_mult": self.residual_mult, "layers": out}
+
+
+@dataclass
+class RotarySpec:
+    """Pair rotation of the first ``dims`` coordinates (2i with 2i+1) by position * base^(-2i/dims); ``scaling``
+    ({factor, original, fast, slow}) blends each frequency with its ``1/factor`` multiple over a ramp (YaRN)."""
+    dims: int
+    base: float
+    scaling: dict | None = None
+
+
+@dataclass
+class LatentMixerSpec:
+    """Attention whose keys and values are expanded per head from one cached latent per token, plus one rotated key
+    part shared by all heads.  ``q_rank`` 0: queries come straight from the input; otherwise through a normed latent.
+    ``window`` 0: every earlier key is visible.  ``gate``: the heads' outputs are multiplied by a sigmoid gate."""
+    heads: int
+    dim: int                       # un-rotated query / key size per head
+    rot_dim: int                   # rotated query / key size per head (the key part is shared by the heads)
+    vdim: int
+    kv_rank: int
+    q_rank: int
+    window: int
+    scale: float
+    rot: RotarySpec
+    gate: bool
+
+    @property
+    def cache_width(self) -> int:
+        return self.kv_rank + self.rot_dim
+
+
+@dataclass
+class RidevikLayerSpec:
+    type: str                      # "latent_attention" | "latent_attention_2"
+    mixer: LatentMixerSpec
+    mlp: FeedForwardSpec | None
+    weights_of: int | None = None  # this layer runs another layer's tensors over a cache and state of its own
+
+
+@dataclass
+class RidevikConfig:
+    """``config.json`` of a Ridevik checkpoint: a decoder-only token model whose layers (listed one by one, each with
+    its own sizes) read the 32-bit residual stream itself, token-shifted for the mixer, and add their output after a
+    grouped RMS norm.  Mixers are latent attentions in two variants; feed-forwards are dense (xIELU, biases) or a
+    softmax-over-chosen mixture of gated experts, or absent.  A layer may reuse an earlier layer's tensors."""
+    architecture: str
+    vocab: int
+    width: int
+    embedding_scale: float
+    norm_eps: float
+    norm_groups: int
+    layers: list
+    max_positions = None           # positions enter through rotations only: no table bounds them
+
+    page_multiple = 16
+
+    MIXER_TYPES = ("latent_attention", "latent_attention_2")
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "RidevikConfig":
+        layers = []
+        for i, ld in enumerate(d["layers"]):
+            if ld["type"] not in cls.MIXER_TYPES:
+                raise ValueError(f"layer {i}: unknown mixer type {ld['type']!r}")
+            m = ld["mixer"]
+            r = m["rot"]
+            rot = RotarySpec(int(r["dims"]), float(r["base"]), dict(r["scaling"]) if r.get("scaling") else None)
+            mixer = LatentMixerSpec(heads=int(m["heads"]), dim=int(m["dim"]), rot_dim=int(m["rot_dim"]), vdim=int(m["vdim"]),
+                                    kv_rank=int(m["kv_rank"]), q_rank=int(m.get("q_rank") or 0),
+                                    window=int(m["mask"]["size"]) if m.get("mask") else 0, scale=float(m["scale"]), rot=rot,
+                                    gate=ld["type"] == "latent_attention")
+            if rot.dims > mixer.rot_dim or rot.dims % 2:
+                raise ValueError(f"layer {i}: {rot.dims} rotated dimensions in a part of {mixer.rot_dim}")
+            f = ld.get("mlp")
+            mlp = None
+            if f is not None:
+                if f["kind"] == "dense":
+                    mlp = FeedForwardSpec("dense", int(f["ff"]), act="xielu", bias=True)
+                elif f["kind"] == "moe":
+                    ro = f["router"]
+                    mlp = FeedForwardSpec("moe", int(f["expert"]["ff"]), int(ro["experts"]), int(ro["top"]), act="silu_gate",
+                                          router="softmax_chosen")
+                else:
+                    raise ValueError(f"layer {i}: unknown feed-forward kind {f['kind']!r}")
+            src = ld.get("weights_of")
+            if src is not None and not (0 <= int(src) < i and d["layers"][int(src)].get("weights_of") is None):
+                raise ValueError(f"layer {i}: weights_of {src} must name an earlier layer with tensors of its own")
+            layers.append(RidevikLayerSpec(ld["type"], mixer, mlp, None if src is None else int(src)))
+        c = cls(architecture=d["architecture"], vocab=int(d["vocab"]), width=int(d["width"]),
+                embedding_scale=float(d["embedding"]["scale"]), norm_eps=float(d["norm"]["eps"]),
+                norm_groups=int(d["norm"].get("groups", 1)), layers=layers)
+        if c.width % c.norm_groups:
+            raise ValueError(f"width {c.width} does not split into {c.norm_groups} norm groups")
+        return c
+
+    @classmethod
+    def from_pretrained(cls, model_dir: str) -> "RidevikConfig":
+        with open(os.path.join(model_dir, "config.json")) as f:
+            return cls.from_dict(json.load(f))
+
+    def to_dict(self) -> dict:
+        out = []
+        for l in self.layers:
+            m = l.mixer
+            mix = {"heads": m.heads, "dim": m.dim, "rot_dim": m.rot_dim, "vdim": m.vdim, "kv_rank": m.kv_rank, "scale": m.scale,
+                   "rot": {"dims": m.rot.dims, "base": m.rot.base}}
+            if m.rot.scaling:
+                mix["rot"]["scaling"] = dict(m.rot.scaling)
+            if m.q_rank:
+                mix["q_rank"] = m.q_rank
+            if m.window:
+                mix["mask"] = {"size": m.window}
+            mlp = None
+            if l.mlp is not None and l.mlp.kind == "dense":
+                mlp = {"kind": "dense", "ff": l.mlp.ff}
+            elif l.mlp is not None:
+                mlp = {"kind": "moe", "expert": {"ff": l.mlp.ff}, "router": {"experts": l.mlp.experts, "top": l.mlp.top}}
+            entry = {"type": l.type, "mixer": mix, "mlp": mlp}
+            if l.weights_of is not None:
+                entry["weights_of"] = l.weights_of
+            out.append(entry)
+        return {"architecture": self.architecture, "vocab": self.vocab, "width": self.width,
+                "embedding": {"scale": self.embedding_scale}, "norm": {"eps": self.norm_eps, "groups": self.norm_groups},
+                "layers": out}
 
 
 def load_model_config(model_dir: str):

@@ -423,7 +423,8 @@ constexpr int ROUTE_MAX_EXPERTS = 256;
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router /* [E, cols] */, int32_t* __restrict__ top_idx,
-                 float* __restrict__ top_w, int n_tokens, int cols, int E, int top, float scale) {
+                 float* __restrict__ top_w, int n_tokens, int cols, int E, int top, float scale,
+                 const float* __restrict__ bias /* [E] or null */, int softmax_chosen) {
   __shared__ float score[ROUTE_WARPS][ROUTE_MAX_EXPERTS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n = blockIdx.x * ROUTE_WARPS + warp;
@@ -435,16 +436,21 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router /* [E
     for (int c = lane; c < cols; c += 32) acc += to_f(hr[c]) * wr[c];
     acc = warp_sum(acc);
     if (lane == 0) {
-      const float sc = 1.0f / (1.0f + expf(-acc));
-      score[warp][e] = sc >= 0.f ? sc : 0.f;             // a NaN input still yields valid expert ids
+      if (softmax_chosen) {
+        const float sc = acc + (bias != nullptr ? bias[e] : 0.f);
+        score[warp][e] = sc >= -3.0e38f ? sc : -3.0e38f;  // a NaN input still yields valid expert ids
+      } else {
+        const float sc = 1.0f / (1.0f + expf(-acc));
+        score[warp][e] = sc >= 0.f ? sc : 0.f;
+      }
     }
   }
   __syncwarp();
-  float sum = 0.f;
+  float sum = 0.f, first = 0.f;
   float chosen_s = 0.f;          // lane k keeps the k-th choice
   int chosen_e = 0;
   for (int k = 0; k < top; ++k) {
-    float best = -1.f;
+    float best = -INFINITY;
     int be = 0x7fffffff;
     for (int e = lane; e < E; e += 32) {
       const float s = score[warp][e];
@@ -456,14 +462,16 @@ moe_route_kernel(const T* __restrict__ h, const float* __restrict__ router /* [E
       const int oe = __shfl_xor_sync(0xffffffffu, be, o);
       if (ob > best || (ob == best && oe < be)) { best = ob; be = oe; }
     }
+    if (k == 0) first = best;
+    if (softmax_chosen) best = expf(best - first);       // weights: the softmax over the chosen logits only
     if (lane == (k & 31)) { chosen_s = best; chosen_e = be; }
     sum += best;
-    if (lane == 0) score[warp][be] = -2.f;
+    if (lane == 0) score[warp][be] = -INFINITY;
     __syncwarp();
   }
   if (lane < top) {
     top_idx[static_cast<size_t>(n) * top + lane] = chosen_e;
-    top_w[static_cast<size_t>(n) * top + lane] = chosen_s / (sum + 1e-20f) * scale;
+    top_w[static_cast<size_t>(n) * top + lane] = softmax_chosen ? chosen_s / sum * scale : chosen_s / (sum + 1e-20f) * scale;
   }
 }
 
@@ -623,8 +631,8 @@ extern "C" int b2tts_conv_headnorm_kvwrite(const void* u, int64_t u_stride, cons
 }
 
 extern "C" int b2tts_moe_route(const void* h, const float* router, int32_t* top_idx, float* top_w, int32_t* offsets,
-                               int32_t* sorted_pair, int n_tokens, int cols, int experts, int top, float scale, int dtype,
-                               void* stream) {
+                               int32_t* sorted_pair, int n_tokens, int cols, int experts, int top, float scale,
+                               const float* bias, int softmax_chosen, int dtype, void* stream) {
   using namespace b2;
   B2_REQUIRE(n_tokens >= 0 && cols > 0 && experts > 0 && top > 0 && top <= experts, B2TTS_EINVAL, "moe_route: bad sizes");
   B2_REQUIRE(experts <= ROUTE_MAX_EXPERTS && top <= 32, B2TTS_EUNSUPPORTED, "moe_route: experts %d > %d or top %d > 32", experts,
@@ -637,10 +645,10 @@ extern "C" int b2tts_moe_route(const void* h, const float* router, int32_t* top_
     const int grid = (n_tokens + ROUTE_WARPS - 1) / ROUTE_WARPS;
     if (dtype == B2TTS_DTYPE_BF16)
       moe_route_kernel<__nv_bfloat16><<<grid, ROUTE_WARPS * 32, 0, st>>>(static_cast<const __nv_bfloat16*>(h), router, top_idx, top_w,
-                                                                          n_tokens, cols, experts, top, scale);
+                                                                          n_tokens, cols, experts, top, scale, bias, softmax_chosen);
     else
       moe_route_kernel<float><<<grid, ROUTE_WARPS * 32, 0, st>>>(static_cast<const float*>(h), router, top_idx, top_w, n_tokens, cols,
-                                                                 experts, top, scale);
+                                                                 experts, top, scale, bias, softmax_chosen);
     B2_CHECK_LAUNCH("moe_route");
   }
   moe_group_kernel<<<1, 1024, 0, st>>>(top_idx, offsets, sorted_pair, n_tokens * top, experts);

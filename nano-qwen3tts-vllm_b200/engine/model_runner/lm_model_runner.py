@@ -4,8 +4,9 @@ decoded tokens together, over a paged K/V pool with per-layer shapes and a pool 
 Differences from the embedding-driven runners of this package, all behind the same ``ModelRunner`` construction:
   * the batch is a list of (sequence, tokens to run) - there is no separate prefill and decode layout; the decode
     step (every row one token) is additionally captured as CUDA graphs per batch size;
-  * K and V pages are allocated per layer ([pages, page, kv_heads * dim] and [pages, page, kv_heads * vdim]), since a
-    layer lists its own head counts and sizes;
+  * paged tensors and state slots are allocated per layer run from the model's ``cache_plan()`` (K and V pages of a
+    layer's own head counts and sizes, or one page of latents; convolution taps, or a token-shift row), since a layer
+    lists its own sizes and a layer that reuses another's weights still has a cache of its own;
   * activations and caches are bfloat16, or float32 when the engine is built with ``dtype="float32"`` (matrix
     products then run as true 32-bit library GEMMs: TF32 is switched off around this runner's calls only)."""
 from __future__ import annotations
@@ -53,9 +54,9 @@ class LMModelRunner(ModelRunner):
 
     def load_model(self, state_dict):
         if isinstance(state_dict, str) and state_dict.startswith("random"):
-            from ...models.bokenex import random_state_dict
+            import importlib
             seed = int(state_dict.split(":")[1]) if ":" in state_dict else 1234
-            state_dict = random_state_dict(self.stack_config, seed)
+            state_dict = importlib.import_module(type(self.model).__module__).random_state_dict(self.stack_config, seed)
         if state_dict is None and self.config.model:
             path = os.path.join(self.config.model, "model.safetensors")
             if os.path.exists(path):
@@ -78,25 +79,26 @@ class LMModelRunner(ModelRunner):
 
     def kv_block_bytes(self) -> int:
         el = 4 if self.param_dtype == torch.float32 else 2
-        return sum(self.block_size * l.mixer.kv_heads * (l.mixer.dim + l.mixer.vdim) * el for l in self.stack_config.layers)
+        return sum(self.block_size * w * el for plan in self.model.cache_plan() for w in plan["paged"])
 
     def allocate_kv_cache(self):
+        """The model says what every layer run needs (``cache_plan``): paged tensors [pages, page, width] that share one
+        block table, and per-sequence state tensors [slots, ...] that share one slot id.  A layer that reuses another
+        layer's weights still gets tensors of its own."""
         cfg = self.config
         if cfg.num_kvcache_blocks <= 0:
             free, _ = torch.cuda.mem_get_info(self.device)
             blocks = int(free * cfg.gpu_memory_utilization * 0.9) // max(self.kv_block_bytes(), 1)
             cfg.num_kvcache_blocks = max(1, min(blocks, self.max_bs * self.max_blocks))
         slots = cfg.max_state_slots or cfg.max_num_seqs
-        self.kv_cache, self.conv_state = [], []
-        for layer, (attn, conv) in zip(self.stack_config.layers, self.model.cache_modules()):
-            m = layer.mixer
-            k = torch.zeros(cfg.num_kvcache_blocks, self.block_size, m.kv_heads * m.dim, dtype=self.param_dtype, device=self.device)
-            v = torch.zeros(cfg.num_kvcache_blocks, self.block_size, m.kv_heads * m.vdim, dtype=self.param_dtype, device=self.device)
-            attn.k_cache, attn.v_cache = k, v
-            st = torch.zeros(slots, max(m.conv - 1, 1), m.channels, dtype=self.param_dtype, device=self.device)
-            conv.state = st
-            self.kv_cache.append((k, v))
-            self.conv_state.append(st)
+        self.kv_cache, self.seq_state = [], []
+        for run, plan in enumerate(self.model.cache_plan()):
+            paged = [torch.zeros(cfg.num_kvcache_blocks, self.block_size, w, dtype=self.param_dtype, device=self.device)
+                     for w in plan["paged"]]
+            state = [torch.zeros(slots, *shape, dtype=dt or self.param_dtype, device=self.device) for shape, dt in plan["state"]]
+            self.model.bind_cache(run, paged, state)
+            self.kv_cache.append(paged)
+            self.seq_state.append(state)
 
     # ------------------------------------------------------------------ the step
     def true_float32(self):

@@ -30,3 +30,22 @@ class ReluSquared(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return nat.relu_sq_(x)
+
+
+class XIELU(nn.Module):
+    """z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2, with two learned numbers
+    (p, q) kept in float; in place, a bias may be added first (in float, before the activation)."""
+
+    def __init__(self):
+        super().__init__()
+        self.pq = nn.Parameter(torch.zeros(2, dtype=torch.float32), requires_grad=False)
+
+    def forward(self, y: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+        return nat.xielu_(y, bias, self.pq)
+
+
+class GatedSilu(nn.Module):
+    """[gate | up] along the last axis -> silu(gate) * up (bf16 or float32)."""
+
+    def forward(self, gu: torch.Tensor) -> torch.Tensor:
+        return nat.silu_mul(gu)

@@ -74,3 +74,30 @@ class WindowSigmoidAttention(nn.Module):
         nat.window_sigmoid_attn(q, self.k_cache, self.v_cache, out, lay, self.r1, self.r2, self.pb, self.heads,
                                 self.kv_heads, self.dim, self.vdim, self.k_cache.shape[1], self.window, self.scale)
         return out
+
+
+class LatentSinkAttention(nn.Module):
+    """Softmax attention over a paged cache of latents, with a learned per-head sink in the denominator.
+
+    A cached row is [c | kr]: the normed key/value latent (``kv_rank``) and the rotated key part all heads share
+    (``rot_dim``).  Head h's key is [W_uk,h c | kr], its value W_uv,h c.  Neither is materialised: the caller hands in
+    queries already multiplied by W_uk,h^T (``ql`` [heads, n, kv_rank]) and gets back the attention-weighted sums of
+    latents ([heads, n, kv_rank]), to which it applies W_uv,h.  ``window`` 0 = causal without a window.  The cache holds
+    this step's rows already (``nat.latent_prep`` wrote them), so prompt portions and decoded tokens run in one launch."""
+
+    def __init__(self, heads: int, kv_rank: int, rot_dim: int, window: int, scale: float, rotary):
+        super().__init__()
+        self.heads, self.kv_rank, self.rot_dim, self.window, self.scale, self.rotary = heads, kv_rank, rot_dim, window, scale, rotary
+        self.sink = nn.Parameter(torch.zeros(heads, dtype=torch.float32), requires_grad=False)
+        self.path = nat.LATENT_ATTN_AUTO
+
+    def forward(self, ql: torch.Tensor, qr: torch.Tensor, qr_strides, cache: torch.Tensor) -> torch.Tensor:
+        """ql [heads, n, kv_rank] contiguous; qr: any tensor whose element (t, h, :rot_dim) lies at
+        t * qr_strides[0] + h * qr_strides[1] (the rotary query parts, not yet rotated)."""
+        lay = get_context().step_layout
+        n = ql.shape[1]
+        out = torch.empty_like(ql)
+        nat.latent_attn(ql, (self.kv_rank, n * self.kv_rank), qr, qr_strides, cache, out, (self.kv_rank, n * self.kv_rank),
+                        self.sink, self.rotary.freq, self.rotary.mult, self.rotary.dims, lay, self.heads, self.kv_rank,
+                        self.rot_dim, cache.shape[1], self.window, self.scale, self.path)
+        return out

@@ -40,3 +40,17 @@ class TokenPositionEmbedding(nn.Module):
         nat.embed_pos_norm(tokens, positions, self.embed, self.pos, x, h, norm.gain() if norm is not None else None,
                            norm.eps if norm is not None else 0.0)
         return x, h
+
+
+class ScaledTokenEmbedding(nn.Module):
+    """Token embedding times a constant, written as floats into a 32-bit residual stream."""
+
+    def __init__(self, vocab: int, width: int, scale: float):
+        super().__init__()
+        self.scale = scale
+        self.embed = nn.Parameter(torch.empty(vocab, width), requires_grad=False)
+
+    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+        x = torch.empty(tokens.shape[0], self.embed.shape[1], dtype=torch.float32, device=tokens.device)
+        nat.embed_scale(tokens, self.embed, self.scale, x)
+        return x

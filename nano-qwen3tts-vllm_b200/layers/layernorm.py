@@ -43,3 +43,27 @@ class GainRMSNorm(nn.Module):
 
     def forward(self, x: torch.Tensor, dtype: torch.dtype, rows: torch.Tensor | None = None) -> torch.Tensor:
         return nat.gather_gain_norm(x, rows, self.gain(), self.eps, dtype)
+
+
+class GroupRMSNorm(nn.Module):
+    """RMS norm in groups: the vector is cut into ``groups`` equal consecutive parts, each divided by its own
+    sqrt(mean(part^2) + eps), the whole multiplied by a weight vector (kept in float).  In a model it sits on a
+    sublayer's OUTPUT and rides in the residual update: ``add_to`` does x += norm(y) on a 32-bit stream, with y a
+    dense output ``a`` and / or the weighted sum of per-choice expert outputs ``z`` (weights ``zw``).  ``forward`` is
+    the stand-alone form over a subset of rows (the final norm before the head)."""
+
+    def __init__(self, width: int, groups: int = 1, eps: float = 1e-6):
+        super().__init__()
+        assert width % groups == 0
+        self.groups, self.eps = groups, eps
+        self.weight = nn.Parameter(torch.ones(width, dtype=torch.float32), requires_grad=False)
+
+    def add_to(self, x: torch.Tensor, a=None, z=None, zw=None, copy_dtype: torch.dtype | None = None, dtype=None):
+        """x [n, width] float, updated in place.  Returns the new x in ``copy_dtype`` (or None)."""
+        dtype = dtype or (a.dtype if a is not None else z.dtype)
+        copy = torch.empty(x.shape, dtype=copy_dtype, device=x.device) if copy_dtype is not None else None
+        nat.group_norm_residual(x, a, z, zw, self.weight, self.groups, self.eps, copy, dtype)
+        return copy
+
+    def forward(self, x: torch.Tensor, dtype: torch.dtype, rows: torch.Tensor | None = None) -> torch.Tensor:
+        return nat.gather_group_norm(x, rows, self.weight, self.groups, self.eps, dtype)

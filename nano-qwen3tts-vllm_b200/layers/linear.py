@@ -159,6 +159,14 @@ def linear_relu_sq(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return nat.relu_sq_(linear(x, weight))
 
 
+def per_head_linear(x: torch.Tensor, weight: torch.Tensor, transpose_weight: bool = False) -> torch.Tensor:
+    """One small projection per head, all heads in one strided-batched library GEMM (cuBLAS through ``torch.bmm``):
+    x [heads, n, k] (any strides) and weight [heads, k, m] (or [heads, m, k] with ``transpose_weight``) -> [heads, n, m]."""
+    if not x.is_cuda:
+        raise RuntimeError("libb200tts: per_head_linear() needs CUDA tensors (there is no CPU path)")
+    return torch.bmm(x, weight.transpose(1, 2) if transpose_weight else weight)
+
+
 class LinearBase(nn.Module):
     def __init__(self, input_size: int, output_size: int, bias: bool = False, tp_dim: int | None = None):
         super().__init__()

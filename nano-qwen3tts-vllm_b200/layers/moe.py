@@ -1,24 +1,36 @@
-"""Mixture-of-experts feed-forward with a sigmoid top-k router.
+"""Mixture-of-experts feed-forwards with a top-k router.
 
-Router logits are computed in float; the ``top`` experts with the largest sigmoid scores are chosen, and their
-weights are the scores divided by their sum (+ 1e-20) times ``scale``.  Experts are two-matrix feed-forwards with a
-squared-ReLU activation, stored stacked ([experts, ff, width] / [experts, width, ff]) so that ONE grouped launch runs
-all of them over the (token, choice) pairs sorted by expert - for a prompt portion of thousands of tokens and for a
-decode step of a few rows per expert alike, with no group size ever read back to the host.  ``forward`` returns the
-per-pair outputs and weights;
-the weighted sum over a token's choices is taken, in a fixed order, by the residual kernel that consumes them."""
+Router scores are computed in float.  Two routers: sigmoid scores, the chosen ones divided by their sum (+ 1e-20)
+times ``scale``; or logits (plus a bias) whose chosen ones are soft-maxed among themselves.  Two experts: two matrices
+with a squared ReLU, or three with a SiLU gate.  Experts are stored stacked ([experts, ff or 2 ff, width] /
+[experts, width, ff]) so that ONE grouped launch runs all of them over the (token, choice) pairs sorted by expert -
+for a prompt portion of thousands of tokens and for a decode step of a few rows per expert alike, with no group size
+ever read back to the host.  ``forward`` returns the per-pair outputs and weights; the weighted sum over a token's
+choices is taken, in a fixed order, by the residual kernel that consumes them."""
 import torch
 from torch import nn
 
 from .. import _native as nat
 
 
-class SigmoidTopKMoE(nn.Module):
-    def __init__(self, width: int, ff: int, experts: int, top: int, scale: float):
+class TopKMoE(nn.Module):
+    """The shared machinery: route, group by expert, two grouped launches.  ``router_kind`` "sigmoid" (scores divided
+    by the sum of the chosen, times ``scale``) or "softmax_chosen" (logits plus an optional bias; weights are the
+    softmax over the chosen logits only).  ``gated``: an expert is W_down (silu(W_gate h) * (W_up h)) with gate and up
+    stacked in one [experts, 2 ff, width] tensor; otherwise W_down relu(W_up h)^2."""
+
+    def __init__(self, width: int, ff: int, experts: int, top: int, scale: float = 1.0, router_kind: str = "sigmoid",
+                 router_bias: bool = False, gated: bool = False):
         super().__init__()
+        assert router_kind in ("sigmoid", "softmax_chosen")
         self.width, self.ff, self.experts, self.top, self.scale = width, ff, experts, top, scale
+        self.router_kind, self.gated = router_kind, gated
         self.router = nn.Parameter(torch.zeros(experts, width, dtype=torch.float32), requires_grad=False)
-        self.up = nn.Parameter(torch.empty(experts, ff, width), requires_grad=False)
+        if router_bias:
+            self.router_bias = nn.Parameter(torch.zeros(experts, dtype=torch.float32), requires_grad=False)
+        else:
+            self.register_parameter("router_bias", None)
+        self.up = nn.Parameter(torch.empty(experts, (2 if gated else 1) * ff, width), requires_grad=False)
         self.down = nn.Parameter(torch.empty(experts, width, ff), requires_grad=False)
 
     def route(self, h: torch.Tensor):
@@ -27,7 +39,8 @@ class SigmoidTopKMoE(nn.Module):
         top_w = torch.empty(n, self.top, dtype=torch.float32, device=dev)
         offsets = torch.empty(self.experts + 1, dtype=torch.int32, device=dev)
         sorted_pair = torch.empty(n * self.top, dtype=torch.int32, device=dev)
-        nat.moe_route(h, self.router, top_idx, top_w, offsets, sorted_pair, self.top, self.scale)
+        nat.moe_route(h, self.router, top_idx, top_w, offsets, sorted_pair, self.top, self.scale, bias=self.router_bias,
+                      softmax_chosen=self.router_kind == "softmax_chosen")
         return top_idx, top_w, offsets, sorted_pair
 
     def forward(self, h: torch.Tensor):
@@ -35,8 +48,25 @@ class SigmoidTopKMoE(nn.Module):
         n = h.shape[0]
         pairs = n * self.top
         _, top_w, offsets, sorted_pair = self.route(h)
-        y = torch.empty(pairs, self.ff, dtype=h.dtype, device=h.device)
-        nat.grouped_gemm(h, self.up, y, offsets, sorted_pair, pairs, self.top, in_by_token=True, out_by_pair=False, act=1)
+        if self.gated:
+            gu = torch.empty(pairs, 2 * self.ff, dtype=h.dtype, device=h.device)
+            nat.grouped_gemm(h, self.up, gu, offsets, sorted_pair, pairs, self.top, in_by_token=True, out_by_pair=False, act=0)
+            y = nat.silu_mul(gu)
+        else:
+            y = torch.empty(pairs, self.ff, dtype=h.dtype, device=h.device)
+            nat.grouped_gemm(h, self.up, y, offsets, sorted_pair, pairs, self.top, in_by_token=True, out_by_pair=False, act=1)
         z = torch.empty(pairs, self.width, dtype=h.dtype, device=h.device)
         nat.grouped_gemm(y, self.down, z, offsets, sorted_pair, pairs, self.top, in_by_token=False, out_by_pair=True, act=0)
         return z, top_w
+
+
+class SigmoidTopKMoE(TopKMoE):
+    def __init__(self, width: int, ff: int, experts: int, top: int, scale: float):
+        super().__init__(width, ff, experts, top, scale, "sigmoid", False, False)
+
+
+class SoftmaxTopKGatedMoE(TopKMoE):
+    """Router logits W_r h + b in float, the ``top`` largest chosen, weights = softmax over the chosen; gated SiLU experts."""
+
+    def __init__(self, width: int, ff: int, experts: int, top: int):
+        super().__init__(width, ff, experts, top, 1.0, "softmax_chosen", True, True)

@@ -66,3 +66,30 @@ def get_rope(head_size: int, rotary_dim: int, max_position: int, base: float, ro
         return TalkerRotaryEmbedding(head_size, rotary_dim, max_position, base, rope_scaling["mrope_section"],
                                      rope_scaling.get("interleaved", rope_scaling.get("mrope_interleaved", False)))
     return RotaryEmbedding(head_size, rotary_dim, max_position, base)
+
+
+class PairRotary(nn.Module):
+    """Frequencies of a pair rotation (coordinate 2i with 2i+1) of the first ``dims`` coordinates of a vector:
+    f_i = base^(-2i/dims).  With ``scaling`` = {factor, original, fast, slow} (YaRN): with
+    turns(t) = dims ln(original / (2 pi t)) / (2 ln base), lo = max(floor(turns(fast)), 0),
+    hi = min(ceil(turns(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency is
+    f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and sin are multiplied by ``mult`` = 0.1 ln(factor) + 1.
+    The table is computed in float64 and kept as float; the kernels that rotate (``nat.latent_prep`` for keys,
+    ``nat.latent_attn`` for queries) form the angle position * f_i in float."""
+
+    def __init__(self, dims: int, base: float, scaling: dict | None = None):
+        super().__init__()
+        import math
+        assert dims % 2 == 0
+        i = torch.arange(dims // 2, dtype=torch.float64)
+        f = torch.as_tensor(float(base), dtype=torch.float64) ** (-2.0 * i / max(dims, 1))
+        self.dims, self.mult = dims, 1.0
+        if scaling:
+            factor, orig = float(scaling["factor"]), float(scaling["original"])
+            turns = lambda t: dims * math.log(orig / (2 * math.pi * t)) / (2 * math.log(base))
+            lo = max(math.floor(turns(float(scaling["fast"]))), 0)
+            hi = min(math.ceil(turns(float(scaling["slow"]))), dims - 1)
+            ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0, 1)
+            f = f / factor * ramp + f * (1 - ramp)
+            self.mult = 0.1 * math.log(factor) + 1.0
+        self.register_buffer("freq", f.to(torch.float32), persistent=False)

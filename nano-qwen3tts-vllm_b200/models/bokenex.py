@@ -116,8 +116,18 @@ class BokenexForCausalLM(nn.Module):
 
     # ------------------------------------------------------------------ weights
     def cache_modules(self):
-        """(attention, convolution) module pairs in layer order: what the runner binds cache and state to."""
+        """(attention, convolution) module pairs in layer order: what cache and state are bound to."""
         return [(l.mix.attn, l.mix.conv) for l in self.layers]
+
+    def cache_plan(self) -> list[dict]:
+        """Per layer: widths of its paged tensors (K, V) and the shape (after the slot axis) of its convolution state."""
+        return [{"paged": [l.mixer.kv_heads * l.mixer.dim, l.mixer.kv_heads * l.mixer.vdim],
+                 "state": [((max(l.mixer.conv - 1, 1), l.mixer.channels), None)]} for l in self.config.layers]
+
+    def bind_cache(self, run: int, paged: list, state: list):
+        attn, conv = self.cache_modules()[run]
+        attn.k_cache, attn.v_cache = paged
+        conv.state = state[0]
 
     def load_state_dict(self, state_dict, strict=True):
         """Checkpoint names: ``embed``, ``pos``, ``l<i>.norm1``, ``l<i>.mix.{q,k,v,o}``, ``l<i>.mix.{q,k,v}.conv``,

@@ -52,6 +52,11 @@ register(Architecture("Bokenex", ".config:BokenexConfig", ".models.bokenex:Boken
                       ".engine.llm_engine.lm_engine:CausalLMEngine"))
 
 
+register(Architecture("Ridevik", ".config:RidevikConfig", ".models.ridevik:RidevikForCausalLM",
+                      ".engine.model_runner.lm_model_runner:LMModelRunner",
+                      ".engine.llm_engine.lm_engine:CausalLMEngine"))
+
+
 def resolve(config: dict) -> Architecture:
     name = config.get("architecture")
     if name is None and "talker_config" in config:
