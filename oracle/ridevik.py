@@ -15,10 +15,6 @@ import math
 import torch
 
 
-def gelu_tanh(z):
-    return 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def rms_norm(x, weight, eps):
     """x / sqrt(mean(x^2) + eps) * weight over the last axis."""
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * weight
@@ -167,3 +163,87 @@ def forward(sd: dict, config: dict, tokens, dtype=torch.float64, layers_out: lis
         if layers_out is not None:
             layers_out.append(x.clone())
     return grouped_rms_norm(x, sd["final.norm"], eps, groups) @ sd["head"].T
+
+
+# ------------------------------------------------------------------------------------------------ test material
+def random_config(seed: int = 0, *, width=48, vocab=61, n_layers=4, heads=(3, 2), dim=(8, 16), rot_dim=(8, 4), rot_dims=None,
+                  vdim=(16, 8), kv_rank=(24, 16), q_rank=12, window=9, groups=2, ff=40, expert_ff=24, experts=5, top=2,
+                  kinds=("dense", "moe", None, "moe"), types=("latent_attention_2", "latent_attention"), share=None,
+                  scaling=True, embedding_scale=3.0, eps=1e-5) -> dict:
+    """A small config.json dict.  ``types`` / ``kinds`` cycle over the layers; index 0 of the size pairs belongs to
+    "latent_attention_2", index 1 to "latent_attention".  ``share`` = {layer: earlier layer whose tensors it reuses}."""
+    layers = []
+    for i in range(n_layers):
+        t = types[i % len(types)]
+        k = 1 if t == "latent_attention" else 0
+        rd = rot_dim[k]
+        mixer = {"heads": heads[k], "dim": dim[k], "rot_dim": rd, "vdim": vdim[k], "kv_rank": kv_rank[k],
+                 "scale": (dim[k] + rd) ** -0.5 * (1.0 + 0.25 * k),
+                 "rot": {"base": 10000.0 if k == 0 else 500.0, "dims": rd if rot_dims is None else rot_dims[k]}}
+        if k == 1:
+            mixer["q_rank"] = q_rank
+            mixer["mask"] = {"size": window}
+            if scaling:
+                mixer["rot"]["scaling"] = {"factor": 3.0, "original": 16, "fast": 4.0, "slow": 0.5}
+        kind = kinds[i % len(kinds)]
+        mlp = None
+        if kind == "dense":
+            mlp = {"kind": "dense", "ff": ff}
+        elif kind == "moe":
+            mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top}}
+        layers.append({"type": t, "mixer": mixer, "mlp": mlp})
+    for i, j in (share or {}).items():
+        layers[i] = dict(layers[j], weights_of=j)
+    return {"architecture": "Ridevik", "vocab": vocab, "width": width, "embedding": {"scale": embedding_scale},
+            "norm": {"eps": eps, "groups": groups}, "layers": layers}
+
+
+def random_weights(config: dict, seed: int = 0) -> dict:
+    """Random tensors under the checkpoint's names, rounded to bfloat16 values (held as float64)."""
+    g = torch.Generator().manual_seed(seed)
+    D = config["width"]
+
+    def rnd(*shape, std=1.0, mean=0.0):
+        return (mean + std * torch.randn(shape, generator=g)).to(torch.bfloat16).double()
+
+    sd = {"embed": rnd(config["vocab"], D, std=0.5), "final.norm": rnd(D, mean=1.0, std=0.2), "head": rnd(config["vocab"], D, std=D ** -0.5)}
+    for i, layer in enumerate(config["layers"]):
+        if "weights_of" in layer:
+            continue
+        m, p = layer["mixer"], f"l{i}."
+        H, hd, r = m["heads"], m["dim"] + m["rot_dim"], m["kv_rank"]
+        sd[p + "shift"] = torch.rand(D, generator=g).to(torch.bfloat16).double()
+        sd[p + "norm1"] = rnd(D, mean=0.6, std=0.2)
+        if "q_rank" in m:
+            sd[p + "mix.dq"] = rnd(m["q_rank"], D, std=D ** -0.5)
+            sd[p + "mix.dq.norm"] = rnd(m["q_rank"], mean=1.0, std=0.2)
+            sd[p + "mix.uq"] = rnd(H * hd, m["q_rank"], std=2 * m["q_rank"] ** -0.5)
+        else:
+            sd[p + "mix.q"] = rnd(H * hd, D, std=2 * D ** -0.5)
+        sd[p + "mix.dkv"] = rnd(r + m["rot_dim"], D, std=D ** -0.5)
+        sd[p + "mix.dkv.norm"] = rnd(r, mean=1.0, std=0.2)
+        sd[p + "mix.uk"] = rnd(H * m["dim"], r, std=2 * r ** -0.5)
+        sd[p + "mix.uv"] = rnd(H * m["vdim"], r, std=r ** -0.5)
+        sd[p + "mix.sink"] = rnd(H, std=1.5)
+        if layer["type"] == "latent_attention":
+            sd[p + "mix.g"] = rnd(H * m["vdim"], D, std=D ** -0.5)
+        sd[p + "mix.o"] = rnd(D, H * m["vdim"], std=(H * m["vdim"]) ** -0.5)
+        f = layer["mlp"]
+        if f is None:
+            continue
+        sd[p + "norm2"] = rnd(D, mean=0.6, std=0.2)
+        if f["kind"] == "dense":
+            sd[p + "mlp.up"] = rnd(f["ff"], D, std=D ** -0.5)
+            sd[p + "mlp.up.b"] = rnd(f["ff"], std=0.3)
+            sd[p + "mlp.down"] = rnd(D, f["ff"], std=f["ff"] ** -0.5)
+            sd[p + "mlp.down.b"] = rnd(D, std=0.3)
+            sd[p + "mlp.act"] = rnd(2, std=0.7)
+        else:
+            E, ff = f["router"]["experts"], f["expert"]["ff"]
+            sd[p + "mlp.router"] = rnd(E, D, std=D ** -0.5)
+            sd[p + "mlp.router.b"] = rnd(E, std=0.3)
+            for e in range(E):
+                sd[f"{p}mlp.e{e}.gate"] = rnd(ff, D, std=D ** -0.5)
+                sd[f"{p}mlp.e{e}.up"] = rnd(ff, D, std=D ** -0.5)
+                sd[f"{p}mlp.e{e}.down"] = rnd(D, ff, std=ff ** -0.5)
+    return sd
