@@ -122,6 +122,257 @@ latent_attn_kernel(const LatentAttnArgs a) {
   }
 }
 
+
+// ------------------------------------------------------------------ tensor-core kernel (bf16)
+// A CTA owns 16 query rows: G consecutive tokens of one sequence times up to 16 heads (G = 16 / heads when a sequence
+// has fewer than 16 heads; a decoded token is a tile with one token).  All rows read the SAME cached rows, so a tile of
+// 64 keys is staged once in shared memory ([key][c | kr], two stages filled by 16-byte asynchronous copies through the
+// block table) and used twice: as the key operand of S = Q K^T (each warp scores its own 8 or 16 keys over the whole
+// row width) and, its first r columns read transposed, as the value operand of O += P V (each warp owns r / NW
+// columns of O in registers).  Between the two products the 16 x 64 scores cross shared memory as floats, where the
+// running maximum, the sum and the weights are formed in float (the sink starts the maximum and the sum).
+constexpr int LM_KT = 64;                       // keys per tile
+
+__device__ __forceinline__ void ldsm_x2(uint32_t& r0, uint32_t& r1, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x2_t(uint32_t& r0, uint32_t& r1, const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(smem_u32(p)));
+}
+
+struct LatentMmaSmem {
+  int q_off, k_off, s_off, p_off, st_off, total, ldk;   // byte offsets; ldk = padded row length in elements
+};
+static LatentMmaSmem latent_mma_smem(int r, int dr) {
+  LatentMmaSmem m;
+  const int dkp = (r + dr + 15) / 16 * 16;
+  m.ldk = dkp + 8;
+  m.q_off = 0;
+  m.k_off = 16 * m.ldk * 2;
+  m.s_off = m.k_off + 2 * LM_KT * m.ldk * 2;
+  m.p_off = m.s_off + 16 * LM_KT * 4;
+  m.st_off = m.p_off + 16 * (LM_KT + 8) * 2;
+  m.total = m.st_off + 16 * 4 * 4;
+  return m;
+}
+
+template <int NW, int NT>
+__global__ void __launch_bounds__(NW * 32)
+latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw + sm.q_off);
+  __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(smem_raw + sm.k_off);
+  float* ss = reinterpret_cast<float*>(smem_raw + sm.s_off);
+  __nv_bfloat16* ps = reinterpret_cast<__nv_bfloat16*>(smem_raw + sm.p_off);
+  float* row_m = reinterpret_cast<float*>(smem_raw + sm.st_off);
+  float* row_l = row_m + 16;
+  float* row_alpha = row_l + 16;
+  int* row_pos = reinterpret_cast<int*>(row_alpha + 16);
+  constexpr int THREADS = NW * 32, LDP = LM_KT + 8, SN = LM_KT / 8 / NW;      // SN: score n-tiles per warp
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int ldk = sm.ldk, dkp = ldk - 8, Dk = a.r + a.dr;
+  const int b = blockIdx.y;
+  const int len = a.seq_len[b];
+  const int hpc = min(a.H, 16), hblocks = (a.H + 15) / 16, G = 16 / hpc;
+  const int tile = blockIdx.x / hblocks, hb = blockIdx.x % hblocks;
+  const int tl0 = tile * G;
+  if (tl0 >= len) return;
+  const int pos0 = a.seq_pos0[b], start = a.seq_start[b];
+  const int n_tok = min(G, len - tl0);
+  const int pos_first = pos0 + tl0, pos_last = pos_first + n_tok - 1;
+  const __nv_bfloat16* cache = static_cast<const __nv_bfloat16*>(a.cache);
+  const int32_t* bt = a.block_tables + b * a.bt_stride;
+  const int j_lo = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
+  const int n_tiles = (pos_last - j_lo) / LM_KT + 1;
+
+  auto load_tile = [&](int t, int stage) {
+    __nv_bfloat16* dst = ks + static_cast<size_t>(stage) * LM_KT * ldk;
+    const int cpr = dkp / 8, real = Dk / 8;
+    for (int i = tid; i < LM_KT * cpr; i += THREADS) {
+      const int key = i / cpr, ch = i % cpr;
+      const int j = j_lo + t * LM_KT + key;
+      const bool ok = j <= pos_last && ch < real;
+      const __nv_bfloat16* src = cache;
+      if (ok) src = cache + (static_cast<size_t>(bt[j / a.page]) * a.page + j % a.page) * Dk + ch * 8;
+      cp_async_16(dst + key * ldk + ch * 8, src, ok);
+    }
+    cp_async_commit();
+  };
+  load_tile(0, 0);
+
+  // ---- the 16 query rows: [ql | rotate(qr)] as bf16, zero rows where the tile has no token or head
+  if (tid < 16) {
+    const int tl = tid / hpc, h = hb * 16 + tid % hpc;
+    const bool ok = tl < n_tok && h < a.H;
+    row_pos[tid] = ok ? pos_first + tl : -1;
+    row_m[tid] = ok ? a.sink[h] : 0.f;
+    row_l[tid] = 1.0f;
+  }
+  for (int i = tid; i < 16 * (dkp / 2); i += THREADS) {
+    const int row = i / (dkp / 2), c0 = (i % (dkp / 2)) * 2;
+    const int tl = row / hpc, h = hb * 16 + row % hpc;
+    float v0 = 0.f, v1 = 0.f;
+    if (tl < n_tok && h < a.H) {
+      const int tok = start + tl0 + tl;
+      if (c0 < a.r) {
+        const __nv_bfloat16* ql = static_cast<const __nv_bfloat16*>(a.ql) + tok * a.ql_tok + h * a.ql_head;
+        v0 = __bfloat162float(ql[c0]);
+        v1 = __bfloat162float(ql[c0 + 1]);
+      } else if (c0 < Dk) {
+        const __nv_bfloat16* qr = static_cast<const __nv_bfloat16*>(a.qr) + tok * a.qr_tok + h * a.qr_head;
+        const int d = c0 - a.r;
+        const float u = __bfloat162float(qr[d]), w = __bfloat162float(qr[d + 1]);
+        if (d + 1 < a.rot_dims) {
+          float sn, cs;
+          sincosf(static_cast<float>(pos_first + tl) * a.freq[d / 2], &sn, &cs);
+          sn *= a.rot_mult; cs *= a.rot_mult;
+          v0 = u * cs - w * sn;
+          v1 = w * cs + u * sn;
+        } else { v0 = u; v1 = w; }
+      }
+    }
+    *reinterpret_cast<__nv_bfloat162*>(qs + row * ldk + c0) = __floats2bfloat162_rn(v0, v1);
+  }
+
+  float acc[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+  const int col0 = warp * NT * 8;                                   // this warp's columns of O
+
+  for (int t = 0; t < n_tiles; ++t) {
+    const int stage = t & 1;
+    if (t + 1 < n_tiles) { load_tile(t + 1, stage ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+    __syncthreads();
+    const __nv_bfloat16* kt = ks + static_cast<size_t>(stage) * LM_KT * ldk;
+    // ---- S = Q K^T for this warp's keys
+    float sc[SN][4];
+#pragma unroll
+    for (int i = 0; i < SN; ++i) { sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f; }
+    for (int k0 = 0; k0 < dkp; k0 += 16) {
+      uint32_t af[4];
+      ldsm_x4(af[0], af[1], af[2], af[3], qs + (lane & 15) * ldk + k0 + (lane >> 4) * 8);
+#pragma unroll
+      for (int i = 0; i < SN; ++i) {
+        const int n0 = (warp * SN + i) * 8;
+        uint32_t b0, b1;
+        ldsm_x2(b0, b1, kt + (n0 + (lane & 7)) * ldk + k0 + ((lane >> 3) & 1) * 8);
+        mma_bf16_16816(sc[i], af, b0, b1);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < SN; ++i) {
+      const int n0 = (warp * SN + i) * 8 + (lane & 3) * 2, r0 = lane >> 2;
+      ss[r0 * LM_KT + n0] = sc[i][0];
+      ss[r0 * LM_KT + n0 + 1] = sc[i][1];
+      ss[(r0 + 8) * LM_KT + n0] = sc[i][2];
+      ss[(r0 + 8) * LM_KT + n0 + 1] = sc[i][3];
+    }
+    __syncthreads();
+    // ---- running maximum, sum and weights, in float; a warp takes rows warp, warp + NW, ..
+    for (int row = warp; row < 16; row += NW) {
+      const int rp = row_pos[row];
+      float s[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int j = j_lo + t * LM_KT + lane + 32 * e;
+        const bool vis = j <= rp && (a.window == 0 || rp - j < a.window);
+        s[e] = vis ? ss[row * LM_KT + lane + 32 * e] * a.scale : -INFINITY;
+      }
+      const float m_old = row_m[row];
+      const float m_new = fmaxf(m_old, warp_max(fmaxf(s[0], s[1])));
+      const float p0 = expf(s[0] - m_new), p1 = expf(s[1] - m_new);          // exp(-inf) = 0 for hidden keys
+      const float alpha = expf(m_old - m_new);
+      const float sum = warp_sum(p0 + p1);
+      ps[row * LDP + lane] = __float2bfloat16_rn(p0);
+      ps[row * LDP + lane + 32] = __float2bfloat16_rn(p1);
+      if (lane == 0) {
+        row_m[row] = m_new;
+        row_l[row] = row_l[row] * alpha + sum;
+        row_alpha[row] = alpha;
+      }
+    }
+    __syncthreads();
+    // ---- O = O * alpha + P V, V = the first r columns of the key tile
+    {
+      const float a0 = row_alpha[lane >> 2], a1 = row_alpha[(lane >> 2) + 8];
+#pragma unroll
+      for (int i = 0; i < NT; ++i) { acc[i][0] *= a0; acc[i][1] *= a0; acc[i][2] *= a1; acc[i][3] *= a1; }
+#pragma unroll
+      for (int kk = 0; kk < LM_KT; kk += 16) {
+        uint32_t pf[4];
+        ldsm_x4(pf[0], pf[1], pf[2], pf[3], ps + (lane & 15) * LDP + kk + (lane >> 4) * 8);
+#pragma unroll
+        for (int i = 0; i < NT; ++i) {
+          uint32_t b0, b1;
+          ldsm_x2_t(b0, b1, kt + (kk + (lane & 15)) * ldk + col0 + i * 8);
+          mma_bf16_16816(acc[i], pf, b0, b1);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  // ---- out = O / l
+  {
+    const int r0 = lane >> 2;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int row = r0 + 8 * half;
+      if (row_pos[row] < 0) continue;
+      const int tl = row / hpc, h = hb * 16 + row % hpc;
+      const float inv = 1.0f / row_l[row];
+      __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(a.out) + (start + tl0 + tl) * a.o_tok + h * a.o_head;
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        const int c = col0 + i * 8 + (lane & 3) * 2;
+        orow[c] = __float2bfloat16_rn(acc[i][2 * half] * inv);
+        orow[c + 1] = __float2bfloat16_rn(acc[i][2 * half + 1] * inv);
+      }
+    }
+  }
+}
+
+template <int NW, int NT>
+static cudaError_t launch_latent_mma(const LatentAttnArgs& a, const LatentMmaSmem& sm, dim3 grid, cudaStream_t st) {
+  auto kern = latent_attn_mma_kernel<NW, NT>;
+  if (sm.total > 48 * 1024) {
+    static bool raised = false;                  // one attribute per kernel instance: raise it to the card's limit once
+    if (!raised) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+      if (e != cudaSuccess) return e;
+      raised = true;
+    }
+  }
+  kern<<<grid, NW * 32, sm.total, st>>>(a, sm);
+  return cudaSuccess;
+}
+
+// Sizes the tensor-core kernel takes: r a multiple of 32 (four or eight warps own whole 8-column tiles of O, at most
+// eight each), dr a multiple of 8, everything addressable by 16-byte copies, one tile pair within shared memory.
+static bool latent_mma_fits(const LatentAttnArgs& a, int* nw, int* nt) {
+  if (a.r % 8 || a.dr % 8) return false;
+  const int tiles = a.r / 8;
+  if (tiles % 8 == 0 && tiles / 8 <= 8) { *nw = 8; *nt = tiles / 8; }
+  else if (tiles % 4 == 0 && tiles / 4 <= 8) { *nw = 4; *nt = tiles / 4; }
+  else return false;
+  if (latent_mma_smem(a.r, a.dr).total > 220 * 1024) return false;
+  if (reinterpret_cast<uintptr_t>(a.cache) % 16) return false;
+  if (a.rot_dims % 2 || (a.dr % 2)) return false;
+  return true;
+}
+
+static cudaError_t run_latent_mma(const LatentAttnArgs& a, int nw, int nt, cudaStream_t st) {
+  const LatentMmaSmem sm = latent_mma_smem(a.r, a.dr);
+  const int hpc = a.H < 16 ? a.H : 16, hblocks = (a.H + 15) / 16, G = 16 / hpc;
+  const dim3 grid(static_cast<unsigned>((a.max_new + G - 1) / G) * hblocks, a.n_seqs);
+#define LM_GO(NW, NT) return launch_latent_mma<NW, NT>(a, sm, grid, st)
+#define LM_NT(NW) switch (nt) { case 1: LM_GO(NW, 1); case 2: LM_GO(NW, 2); case 3: LM_GO(NW, 3); case 4: LM_GO(NW, 4); \
+                                case 5: LM_GO(NW, 5); case 6: LM_GO(NW, 6); case 7: LM_GO(NW, 7); case 8: LM_GO(NW, 8); }
+  if (nw == 8) { LM_NT(8) } else { LM_NT(4) }
+#undef LM_NT
+#undef LM_GO
+  return cudaErrorInvalidValue;
+}
+
 }  // namespace lat
 }  // namespace b2
 
@@ -144,7 +395,15 @@ extern "C" int b2tts_latent_attn(const void* ql, int64_t ql_tok, int64_t ql_head
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   LatentAttnArgs a{ql, ql_tok, ql_head, qr, qr_tok, qr_head, cache, out, o_tok, o_head, sink, freq, rot_mult, rot_dims,
                    seq_start, seq_pos0, seq_len, block_tables, bt_stride, n_seqs, max_new, heads, kv_rank, rot_dim, page, window, scale};
-  (void)path;
+  int nw = 0, nt = 0;
+  const bool fits = dtype == B2TTS_DTYPE_BF16 && latent_mma_fits(a, &nw, &nt);
+  B2_REQUIRE(path != 2 || fits, B2TTS_EUNSUPPORTED, "latent_attn: the tensor-core kernel does not take kv_rank %d, rot_dim %d", kv_rank, rot_dim);
+  if (fits && path != 1) {
+    cudaError_t e = run_latent_mma(a, nw, nt, st);
+    if (e != cudaSuccess) return cuda_fail(e, "latent_attn (tensor)");
+    B2_CHECK_LAUNCH("latent_attn (tensor)");
+    return B2TTS_OK;
+  }
   const size_t smem = static_cast<size_t>(LA_WARPS) * (kv_rank + rot_dim) * sizeof(float);
   B2_REQUIRE(smem <= 48 * 1024, B2TTS_EUNSUPPORTED, "latent_attn: key size %d too large", kv_rank + rot_dim);
   const dim3 grid((static_cast<unsigned>(max_new) * heads + LA_WARPS - 1) / LA_WARPS, n_seqs);

@@ -215,6 +215,18 @@ def test_latent_attention_prompts_portions_and_decoded_tokens_in_one_launch(nat,
     assert _attn_case(nat, H, r, dr, window, 64, seqs, seed=H + window + 1, rot_dims=dr - 2) < 2e-5
 
 
+@pytest.mark.parametrize("H,r,dr", [(8, 64, 32), (4, 96, 16), (16, 128, 16), (3, 32, 8), (20, 64, 8), (2, 256, 64), (1, 160, 24)])
+@pytest.mark.parametrize("window", [0, 1, 7, 64, 65, 130])
+def test_tensor_core_latent_attention_against_plain_model_and_plain_kernel(nat, H, r, dr, window):
+    """The bfloat16 tensor-core kernel (forced) on mixed steps: tiles of several tokens (fewer than 16 heads), of one
+    token (16 heads), several head blocks (20 heads), rows of different sequences, keys across many 64-key tiles."""
+    seqs = [(0, 70), (50, 19), (129, 1), (64, 1), (0, 1), (63, 2), (200, 37)]
+    for page, rd in ((16, None), (64, dr - 2)):
+        e_t = _attn_case(nat, H, r, dr, window, page, seqs, dtype=torch.bfloat16, seed=H + window, path=nat.LATENT_ATTN_TENSOR, rot_dims=rd)
+        e_p = _attn_case(nat, H, r, dr, window, page, seqs, dtype=torch.bfloat16, seed=H + window, path=nat.LATENT_ATTN_PLAIN, rot_dims=rd)
+        assert e_t < 2e-2 and e_p < 2e-2, (e_t, e_p)
+
+
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("page", [16, 64])
 @pytest.mark.parametrize("window", [33, 64, 200])
