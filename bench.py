@@ -57,6 +57,9 @@ def parse():
     ap.add_argument("--lm", action="store_true",
                     help="instead of the frame benchmark: prefill / decode throughput of the Bokenex decoder beside the talker "
                          "stack at equal layer sizes, plus its kernels against their rooflines (bench_lm.py); one JSON line")
+    ap.add_argument("--lm-latent", action="store_true",
+                    help="instead of the frame loop: the Ridevik decoder (latent attention) beside Bokenex at equal layer sizes, "
+                         "plus the kernels of both against their rooflines (bench_lm.py); one JSON line")
     return ap.parse_args()
 
 
@@ -480,10 +483,10 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device(device))
     barrier = (lambda: (dist.barrier(), torch.cuda.synchronize())) if dist else None
 
-    if a.lm:
+    if a.lm or a.lm_latent:
         import bench_lm
         if rank == 0:
-            print(json.dumps(bench_lm.main(device)), flush=True)
+            print(json.dumps(bench_lm.main_latent(device) if a.lm_latent else bench_lm.main(device)), flush=True)
         return
 
     total_frames = a.steps + a.warmup + 8

@@ -64,11 +64,11 @@ def _events(fn, iters, warm=3):
     return a.elapsed_time(b) / iters
 
 
-def bench_bokenex(s: dict, moe: bool, device: str) -> dict:
+def bench_bokenex(s: dict, moe: bool, device: str, design: str = "bokenex") -> dict:
     import torch
     from nano_qwen3tts_vllm_b200.engine.llm_engine.lm_engine import CausalLMEngine
     from nano_qwen3tts_vllm_b200.sampling_params import SamplingParams
-    cfg = bokenex_config(s, moe)
+    cfg = bokenex_config(s, moe) if design == "bokenex" else ridevik_config(s, moe)
     pages = DECODE_SEQS * ((DECODE_CTX + 64 + PAGE - 1) // PAGE) + PREFILL_SEQS * (PREFILL_LEN // PAGE + 1)
     eng = CausalLMEngine(cfg, state_dict="random:7", kvcache_block_size=PAGE, num_kvcache_blocks=pages,
                          max_num_seqs=DECODE_SEQS + PREFILL_SEQS, max_model_len=4096, max_num_batched_tokens=16384,
@@ -109,6 +109,24 @@ def bench_bokenex(s: dict, moe: bool, device: str) -> dict:
     out["decode_tok_s"] = round(DECODE_SEQS / ms * 1e3)
     eng.exit()
     return out
+
+
+def ridevik_config(s: dict, moe: bool):
+    """Layers of a real latent-attention model's shape: 16 heads of 128 + 64 (w2048) over a latent of 512, alternating
+    the causal direct-query variant with the windowed, gated, query-latent one; feed-forwards with Bokenex's parameter
+    count (dense: two matrices; experts: three matrices of a third less width)."""
+    from nano_qwen3tts_vllm_b200.config import RidevikConfig
+    d = s["dim"]
+    ff = s["inter"] * 3 // 2
+    mlp = {"kind": "dense", "ff": ff} if not moe else \
+        {"kind": "moe", "expert": {"ff": ff // 3}, "router": {"experts": 16, "top": 2}}
+    base = {"heads": s["heads"], "dim": d, "rot_dim": d // 2, "vdim": d, "kv_rank": 4 * d, "scale": (d + d // 2) ** -0.5}
+    causal = {"type": "latent_attention_2", "mlp": mlp, "mixer": dict(base, rot={"base": 1e6, "dims": d // 2})}
+    window = {"type": "latent_attention", "mlp": mlp,
+              "mixer": dict(base, q_rank=s["width"] // 2, mask={"size": WINDOW},
+                            rot={"base": 1e4, "dims": d // 2, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}})}
+    return RidevikConfig.from_dict({"architecture": "Ridevik", "vocab": 3072, "width": s["width"], "embedding": {"scale": 1.0},
+                                    "norm": {"eps": 1e-6, "groups": 2}, "layers": [causal, window] * (LAYERS // 2)})
 
 
 def bench_talker(s: dict, device: str) -> dict:
@@ -286,6 +304,131 @@ def bench_kernels(device: str) -> dict:
     ms = timed(lambda: torch.nn.functional.linear(hh, wd))
     res["dense GEMM of one projection's FLOPs (cuBLAS)"] = entry(ms, flops=n * top * ff * D * 2)
     return res
+
+
+def bench_latent_kernels(device: str) -> dict:
+    """Ridevik's own kernels at the w2048 layer shape (16 heads, latent 512 + 64 rotated), each after an L2 flush, with
+    the fraction of the measured roofline; the like kernels of Bokenex come from ``bench_kernels`` in the same run."""
+    import torch
+    import nano_qwen3tts_vllm_b200._native as nat
+    from nano_qwen3tts_vllm_b200.layers.rotary_embedding import PairRotary
+    hbm, tflops, how = _peaks()
+    dev = torch.device(device)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    BF = torch.bfloat16
+
+    def timed(fn, iters=5):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(iters):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return sorted(ts)[len(ts) // 2]
+
+    class Lay:
+        pass
+
+    def layout(n_seqs, cached, new, pages_per_seq):
+        lay = Lay()
+        i32 = dict(dtype=torch.int32, device=dev)
+        lay.n_seqs, lay.max_new, lay.n_tokens = n_seqs, new, n_seqs * new
+        lay.seq_start = torch.arange(n_seqs, **i32) * new
+        lay.seq_pos0 = torch.full((n_seqs,), cached, **i32)
+        lay.seq_len = torch.full((n_seqs,), new, **i32)
+        lay.seq_slot = torch.arange(n_seqs, **i32)
+        lay.block_tables = torch.arange(n_seqs * pages_per_seq, **i32).view(n_seqs, pages_per_seq).contiguous()
+        pos = (torch.arange(new, **i32) + cached).repeat(n_seqs)
+        lay.positions = pos
+        lay.tok_seq = torch.arange(n_seqs, **i32).repeat_interleave(new)
+        lay.slot_mapping = (lay.tok_seq * pages_per_seq * PAGE + pos).to(torch.int32)
+        return lay
+
+    def entry(ms, bytes_=None, flops=None):
+        e = {"us": round(ms * 1e3, 1)}
+        if bytes_ is not None:
+            e["gbs"] = round(bytes_ / ms / 1e6, 1)
+            e["frac_hbm"] = round(bytes_ / ms / 1e6 / hbm, 3)
+        if flops is not None:
+            e["tflops"] = round(flops / ms / 1e9, 1)
+            e["frac_tensor"] = round(flops / ms / 1e9 / tflops, 4)
+        return e
+
+    H, r, dr, dv, D, qrank = 16, 512, 64, 128, 2048, 1024
+    Dk = r + dr
+    res = {"peaks": {"hbm_gbs": hbm, "bf16_tflops": tflops, "source": how}}
+    rot = PairRotary(dr, 1e4, None).to(dev)
+    sink = torch.zeros(H, device=dev)
+    scale = 192 ** -0.5
+
+    def attn(lay, cache, window):
+        n = lay.n_tokens
+        ql = torch.randn(H, n, r, device=dev).to(BF)
+        qr = torch.randn(n, H * dr, device=dev).to(BF)
+        out = torch.empty_like(ql)
+        return lambda: nat.latent_attn(ql, (r, n * r), qr, (H * dr, dr), cache, out, (r, n * r), sink, rot.freq, 1.0, dr, lay, H, r, dr,
+                                       PAGE, window, scale)
+
+    pps = (DECODE_CTX + PAGE) // PAGE + 1
+    cache = torch.randn(DECODE_SEQS * pps, PAGE, Dk, device=dev).to(BF)
+    lay = layout(DECODE_SEQS, DECODE_CTX, 1, pps)
+    res["latent_attn decode 64x1100 causal"] = entry(timed(attn(lay, cache, 0)), bytes_=DECODE_SEQS * (DECODE_CTX + 1) * Dk * 2)
+    res["latent_attn decode 64x1100 window 1024"] = entry(timed(attn(lay, cache, WINDOW)), bytes_=DECODE_SEQS * WINDOW * Dk * 2)
+    pps = PREFILL_LEN // PAGE
+    lay = layout(PREFILL_SEQS, 0, PREFILL_LEN, pps)
+    n = PREFILL_SEQS * PREFILL_LEN
+    pairs = PREFILL_SEQS * PREFILL_LEN * (PREFILL_LEN + 1) // 2
+    res["latent_attn prefill 4x2048 causal"] = entry(timed(attn(lay, cache, 0), iters=3), flops=pairs * H * (Dk + r) * 2)
+    pairs_w = PREFILL_SEQS * sum(min(i + 1, WINDOW) for i in range(PREFILL_LEN))
+    res["latent_attn prefill 4x2048 window 1024"] = entry(timed(attn(lay, cache, WINDOW), iters=3), flops=pairs_w * H * (Dk + r) * 2)
+    # ---- latent preparation: norms, key rotation, cache write
+    C = qrank + Dk + H * dv
+    u = torch.randn(n, C, device=dev).to(BF)
+    cq = torch.empty(n, qrank, dtype=BF, device=dev)
+    wq, wkv = torch.ones(qrank, device=dev), torch.ones(r, device=dev)
+    ms = timed(lambda: nat.latent_prep(u, 0, qrank, cq, wq, wkv, rot.freq, 1.0, lay, cache, qrank, r, dr, dr, 1e-6))
+    res["latent_prep 8192 tokens"] = entry(ms, bytes_=n * (qrank + Dk) * 2 * 2)
+    # ---- token shift, residual + group norm, gate
+    x = torch.randn(n, D, device=dev)
+    mu = torch.rand(D, device=dev)
+    st = torch.zeros(PREFILL_SEQS, D, device=dev)
+    hs = torch.empty(n, D, dtype=BF, device=dev)
+    ms = timed(lambda: nat.token_shift(x, mu, st, lay, hs))
+    res["token_shift 8192x2048"] = entry(ms, bytes_=n * D * (4 + 2))
+    a_ = torch.randn(n, D, device=dev).to(BF)
+    w = torch.ones(D, device=dev)
+    cp = torch.empty(n, D, dtype=BF, device=dev)
+    ms = timed(lambda: nat.group_norm_residual(x, a_, None, None, w, 2, 1e-6, cp, BF))
+    res["group_norm_residual 8192x2048"] = entry(ms, bytes_=n * D * (4 + 4 + 2 + 2))
+    v = torch.randn(H, n, dv, device=dev).to(BF)
+    ho = torch.empty(n, H * dv, dtype=BF, device=dev)
+    ms = timed(lambda: nat.gate_heads(v, (dv, n * dv), u[:, qrank + Dk:], ho, H, dv))
+    res["gate_heads 8192 tokens"] = entry(ms, bytes_=n * H * dv * 2 * 3)
+    return res
+
+
+def main_latent(device: str = "cuda:0") -> dict:
+    """``bench.py --lm-latent``: Ridevik beside Bokenex (the package's closest model: a token-id decoder over the same
+    engine) at equal width, layer count and feed-forward parameters, then the kernels of both against their rooflines."""
+    import torch
+    t0 = time.time()
+    out = {"metric": "lm_prefill_decode_throughput", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic (random weights)",
+           "config": {"prefill": f"{PREFILL_SEQS}x{PREFILL_LEN} tokens per step", "decode": f"{DECODE_SEQS} sequences at context {DECODE_CTX}",
+                      "layers": LAYERS, "window": WINDOW, "page": PAGE}, "sizes": {}}
+    for name, s in SIZES.items():
+        row = {"ridevik_dense": bench_bokenex(s, False, device, "ridevik"), "ridevik_moe16top2": bench_bokenex(s, True, device, "ridevik"),
+               "bokenex_dense": bench_bokenex(s, False, device), "bokenex_moe16top2": bench_bokenex(s, True, device)}
+        out["sizes"][name] = row
+        torch.cuda.empty_cache()
+    out["kernels"] = bench_latent_kernels(device)
+    out["like_kernels"] = bench_kernels(device)
+    out["seconds"] = round(time.time() - t0, 1)
+    return out
 
 
 def main(device: str = "cuda:0") -> dict:

@@ -185,16 +185,24 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
   const int j_lo = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
   const int n_tiles = (pos_last - j_lo) / LM_KT + 1;
 
+  // a warp copies whole rows: the page lookup is once per key and uniform over the warp, the lanes stride over the
+  // row's 16-byte chunks; keys past the last query and the padding chunk are zero-filled
   auto load_tile = [&](int t, int stage) {
     __nv_bfloat16* dst = ks + static_cast<size_t>(stage) * LM_KT * ldk;
     const int cpr = dkp / 8, real = Dk / 8;
-    for (int i = tid; i < LM_KT * cpr; i += THREADS) {
-      const int key = i / cpr, ch = i % cpr;
-      const int j = j_lo + t * LM_KT + key;
-      const bool ok = j <= pos_last && ch < real;
-      const __nv_bfloat16* src = cache;
-      if (ok) src = cache + (static_cast<size_t>(bt[j / a.page]) * a.page + j % a.page) * Dk + ch * 8;
-      cp_async_16(dst + key * ldk + ch * 8, src, ok);
+    // lane i looks up the i-th key of this warp: all the table reads of a tile are in flight together
+    long long my = -1;
+    if (lane < LM_KT / NW) {
+      const int j = j_lo + t * LM_KT + warp + lane * NW;
+      if (j <= pos_last) my = (static_cast<long long>(bt[j / a.page]) * a.page + j % a.page) * Dk;
+    }
+#pragma unroll
+    for (int i = 0; i < LM_KT / NW; ++i) {
+      const long long off = __shfl_sync(0xffffffffu, my, i);
+      const bool in = off >= 0;
+      const __nv_bfloat16* src = cache + (in ? off : 0);
+      __nv_bfloat16* drow = dst + (warp + i * NW) * ldk;
+      for (int ch = lane; ch < cpr; ch += 32) cp_async_16(drow + ch * 8, src + ch * 8, in && ch < real);
     }
     cp_async_commit();
   };
@@ -208,18 +216,18 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
     row_m[tid] = ok ? a.sink[h] : 0.f;
     row_l[tid] = 1.0f;
   }
-  for (int i = tid; i < 16 * (dkp / 2); i += THREADS) {
-    const int row = i / (dkp / 2), c0 = (i % (dkp / 2)) * 2;
+  for (int row = warp; row < 16; row += NW) {
     const int tl = row / hpc, h = hb * 16 + row % hpc;
-    float v0 = 0.f, v1 = 0.f;
-    if (tl < n_tok && h < a.H) {
-      const int tok = start + tl0 + tl;
-      if (c0 < a.r) {
-        const __nv_bfloat16* ql = static_cast<const __nv_bfloat16*>(a.ql) + tok * a.ql_tok + h * a.ql_head;
+    const bool ok = tl < n_tok && h < a.H;
+    const int tok = start + tl0 + tl;
+    const __nv_bfloat16* ql = static_cast<const __nv_bfloat16*>(a.ql) + tok * a.ql_tok + h * a.ql_head;
+    const __nv_bfloat16* qr = static_cast<const __nv_bfloat16*>(a.qr) + tok * a.qr_tok + h * a.qr_head;
+    for (int c0 = lane * 2; c0 < dkp; c0 += 64) {
+      float v0 = 0.f, v1 = 0.f;
+      if (ok && c0 < a.r) {
         v0 = __bfloat162float(ql[c0]);
         v1 = __bfloat162float(ql[c0 + 1]);
-      } else if (c0 < Dk) {
-        const __nv_bfloat16* qr = static_cast<const __nv_bfloat16*>(a.qr) + tok * a.qr_tok + h * a.qr_head;
+      } else if (ok && c0 < Dk) {
         const int d = c0 - a.r;
         const float u = __bfloat162float(qr[d]), w = __bfloat162float(qr[d + 1]);
         if (d + 1 < a.rot_dims) {
@@ -230,8 +238,8 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
           v1 = w * cs + u * sn;
         } else { v0 = u; v1 = w; }
       }
+      *reinterpret_cast<__nv_bfloat162*>(qs + row * ldk + c0) = __floats2bfloat162_rn(v0, v1);
     }
-    *reinterpret_cast<__nv_bfloat162*>(qs + row * ldk + c0) = __floats2bfloat162_rn(v0, v1);
   }
 
   float acc[NT][4];
@@ -245,47 +253,71 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
     __syncthreads();
     const __nv_bfloat16* kt = ks + static_cast<size_t>(stage) * LM_KT * ldk;
     // ---- S = Q K^T for this warp's keys
-    float sc[SN][4];
+    float sc[SN][2][4];                          // two accumulators per n-tile: alternate k-steps do not wait on each other
 #pragma unroll
-    for (int i = 0; i < SN; ++i) { sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f; }
-    for (int k0 = 0; k0 < dkp; k0 += 16) {
-      uint32_t af[4];
-      ldsm_x4(af[0], af[1], af[2], af[3], qs + (lane & 15) * ldk + k0 + (lane >> 4) * 8);
+    for (int i = 0; i < SN; ++i)
 #pragma unroll
-      for (int i = 0; i < SN; ++i) {
-        const int n0 = (warp * SN + i) * 8;
-        uint32_t b0, b1;
-        ldsm_x2(b0, b1, kt + (n0 + (lane & 7)) * ldk + k0 + ((lane >> 3) & 1) * 8);
-        mma_bf16_16816(sc[i], af, b0, b1);
+      for (int e = 0; e < 4; ++e) sc[i][0][e] = sc[i][1][e] = 0.f;
+    const __nv_bfloat16* q_lane = qs + (lane & 15) * ldk + (lane >> 4) * 8;
+    const __nv_bfloat16* k_lane = kt + (warp * SN * 8 + (lane & 7)) * ldk + ((lane >> 3) & 1) * 8;
+    for (int k0 = 0; k0 < dkp; k0 += 64) {       // the loads of four k-steps are issued before their products
+      uint32_t af[4][4], bf[4][SN][2];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int k = k0 + 16 * u;
+        if (k < dkp) {
+          ldsm_x4(af[u][0], af[u][1], af[u][2], af[u][3], q_lane + k);
+#pragma unroll
+          for (int i = 0; i < SN; ++i) ldsm_x2(bf[u][i][0], bf[u][i][1], k_lane + i * 8 * ldk + k);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (k0 + 16 * u < dkp) {
+#pragma unroll
+          for (int i = 0; i < SN; ++i) mma_bf16_16816(sc[i][u & 1], af[u], bf[u][i][0], bf[u][i][1]);
+        }
       }
     }
 #pragma unroll
     for (int i = 0; i < SN; ++i) {
       const int n0 = (warp * SN + i) * 8 + (lane & 3) * 2, r0 = lane >> 2;
-      ss[r0 * LM_KT + n0] = sc[i][0];
-      ss[r0 * LM_KT + n0 + 1] = sc[i][1];
-      ss[(r0 + 8) * LM_KT + n0] = sc[i][2];
-      ss[(r0 + 8) * LM_KT + n0 + 1] = sc[i][3];
+      ss[r0 * LM_KT + n0] = sc[i][0][0] + sc[i][1][0];
+      ss[r0 * LM_KT + n0 + 1] = sc[i][0][1] + sc[i][1][1];
+      ss[(r0 + 8) * LM_KT + n0] = sc[i][0][2] + sc[i][1][2];
+      ss[(r0 + 8) * LM_KT + n0 + 1] = sc[i][0][3] + sc[i][1][3];
     }
     __syncthreads();
     // ---- running maximum, sum and weights, in float; a warp takes rows warp, warp + NW, ..
-    for (int row = warp; row < 16; row += NW) {
+    for (int r2 = 2 * warp; r2 < 16; r2 += 2 * NW) {       // half a warp per row, four keys per lane
+      const int row = r2 + (lane >> 4), l16 = lane & 15;
       const int rp = row_pos[row];
-      float s[2];
+      float sv[4];
+      float mx = -INFINITY;
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int j = j_lo + t * LM_KT + lane + 32 * e;
+      for (int e = 0; e < 4; ++e) {
+        const int kk = l16 + 16 * e;
+        const int j = j_lo + t * LM_KT + kk;
         const bool vis = j <= rp && (a.window == 0 || rp - j < a.window);
-        s[e] = vis ? ss[row * LM_KT + lane + 32 * e] * a.scale : -INFINITY;
+        sv[e] = vis ? ss[row * LM_KT + kk] * a.scale : -INFINITY;
+        mx = fmaxf(mx, sv[e]);
       }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
       const float m_old = row_m[row];
-      const float m_new = fmaxf(m_old, warp_max(fmaxf(s[0], s[1])));
-      const float p0 = expf(s[0] - m_new), p1 = expf(s[1] - m_new);          // exp(-inf) = 0 for hidden keys
-      const float alpha = expf(m_old - m_new);
-      const float sum = warp_sum(p0 + p1);
-      ps[row * LDP + lane] = __float2bfloat16_rn(p0);
-      ps[row * LDP + lane + 32] = __float2bfloat16_rn(p1);
-      if (lane == 0) {
+      const float m_new = fmaxf(m_old, mx);
+      float sum = 0.f;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pe = expf(sv[e] - m_new);                                  // exp(-inf) = 0 for hidden keys
+        sum += pe;
+        ps[row * LDP + l16 + 16 * e] = __float2bfloat16_rn(pe);
+      }
+#pragma unroll
+      for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      __syncwarp();
+      if (l16 == 0) {
+        const float alpha = expf(m_old - m_new);
         row_m[row] = m_new;
         row_l[row] = row_l[row] * alpha + sum;
         row_alpha[row] = alpha;
