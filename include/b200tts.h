@@ -495,7 +495,12 @@ B2TTS_API int b2tts_latent_attn(const void* ql, int64_t ql_tok, int64_t ql_head,
                                 float rot_mult, int rot_dims, const int32_t* seq_start, const int32_t* seq_pos0,
                                 const int32_t* seq_len, const int32_t* block_tables, int64_t bt_stride, int n_seqs, int max_new,
                                 int heads, int kv_rank, int rot_dim, int page, int window, float scale, int dtype, int path,
-                                void* stream);
+                                int splits, float* ws, void* stream);
+/* splits > 1 (tensor-core kernel only): each query tile's keys are cut into that many ranges, run by CTAs of their own,
+ * and merged by a second launch; ws holds b2tts_latent_attn_workspace_floats() floats.  b2tts_latent_attn_splits() proposes
+ * a count that fills the GPU for a decode step (1 for anything else). */
+B2TTS_API int b2tts_latent_attn_splits(int n_seqs, int max_new, int heads);
+B2TTS_API size_t b2tts_latent_attn_workspace_floats(int n_seqs, int max_new, int heads, int kv_rank, int splits);
 /* out[t, h * vdim + d] = v[t * v_tok + h * v_head + d] * sigmoid(gate[t * ldg + h * vdim + d]) (gate null: the copy alone). */
 B2TTS_API int b2tts_gate_heads(const void* v, int64_t v_tok, int64_t v_head, const void* gate, int64_t ldg, void* out, int n,
                                int heads, int vdim, int dtype, void* stream);

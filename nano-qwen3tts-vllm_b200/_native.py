@@ -89,7 +89,9 @@ def _load():
         "b2tts_embed_scale": (I, [P, P, P, I, I, I, F, I, P]),
         "b2tts_token_shift": (I, [P, P, P, P, P, P, P, P, P, I, I, I, P]),
         "b2tts_latent_prep": (I, [P, L, I, I, P, P, P, P, F, P, P, P, I, I, I, I, I, F, I, P]),
-        "b2tts_latent_attn": (I, [P, L, L, P, L, L, P, P, L, L, P, P, F, I, P, P, P, P, L, I, I, I, I, I, I, I, F, I, I, P]),
+        "b2tts_latent_attn": (I, [P, L, L, P, L, L, P, P, L, L, P, P, F, I, P, P, P, P, L, I, I, I, I, I, I, I, F, I, I, I, P, P]),
+        "b2tts_latent_attn_splits": (I, [I, I, I]),
+        "b2tts_latent_attn_workspace_floats": (Z, [I, I, I, I, I]),
         "b2tts_gate_heads": (I, [P, L, L, P, L, P, I, I, I, I, P]),
         "b2tts_group_norm_residual": (I, [P, P, P, P, I, P, I, F, P, I, I, I, P]),
         "b2tts_gather_group_norm": (I, [P, P, P, P, I, F, I, I, I, P]),
@@ -817,15 +819,22 @@ LATENT_ATTN_AUTO, LATENT_ATTN_PLAIN, LATENT_ATTN_TENSOR = 0, 1, 2
 
 
 def latent_attn(ql, ql_strides, qr, qr_strides, cache, out, out_strides, sink, freq, rot_mult, rot_dims, lay, heads, kv_rank,
-                rot_dim, page, window, scale, path=LATENT_ATTN_AUTO):
+                rot_dim, page, window, scale, path=LATENT_ATTN_AUTO, splits_override=None):
     """``ql`` / ``qr`` / ``out``: tensors whose element (token t, head h, :) lies at t * strides[0] + h * strides[1]."""
     dt = _act(cache, "cache")
     assert ql.dtype == cache.dtype and qr.dtype == cache.dtype and out.dtype == cache.dtype
-    _check(_load().b2tts_latent_attn(ql.data_ptr(), ql_strides[0], ql_strides[1], qr.data_ptr(), qr_strides[0], qr_strides[1],
-                                     cache.data_ptr(), out.data_ptr(), out_strides[0], out_strides[1], sink.data_ptr(), _ptr(freq),
-                                     rot_mult, rot_dims, lay.seq_start.data_ptr(), lay.seq_pos0.data_ptr(), lay.seq_len.data_ptr(),
-                                     lay.block_tables.data_ptr(), lay.block_tables.stride(0), lay.n_seqs, lay.max_new, heads,
-                                     kv_rank, rot_dim, page, window, scale, dt, path, _stream()), "latent_attn")
+    lib_ = _load()
+    splits, ws = 1, None
+    if cache.dtype == BF16 and path != LATENT_ATTN_PLAIN:
+        splits = lib_.b2tts_latent_attn_splits(lay.n_seqs, lay.max_new, heads) if splits_override is None else splits_override
+        if splits > 1:
+            ws = torch.empty(lib_.b2tts_latent_attn_workspace_floats(lay.n_seqs, lay.max_new, heads, kv_rank, splits),
+                             dtype=F32, device=cache.device)
+    _check(lib_.b2tts_latent_attn(ql.data_ptr(), ql_strides[0], ql_strides[1], qr.data_ptr(), qr_strides[0], qr_strides[1],
+                                  cache.data_ptr(), out.data_ptr(), out_strides[0], out_strides[1], sink.data_ptr(), _ptr(freq),
+                                  rot_mult, rot_dims, lay.seq_start.data_ptr(), lay.seq_pos0.data_ptr(), lay.seq_len.data_ptr(),
+                                  lay.block_tables.data_ptr(), lay.block_tables.stride(0), lay.n_seqs, lay.max_new, heads,
+                                  kv_rank, rot_dim, page, window, scale, dt, path, splits, _ptr(ws), _stream()), "latent_attn")
 
 
 def gate_heads(v, v_strides, gate, out, heads, vdim):

@@ -34,6 +34,8 @@ struct LatentAttnArgs {
   const int32_t *seq_start, *seq_pos0, *seq_len, *block_tables; int64_t bt_stride;
   int n_seqs, max_new, H, r, dr, page, window;
   float scale;
+  int ql_vec;                                    // ql rows can be read 16 bytes at a time
+  int splits; float* ws;                         // key ranges per query tile (tensor-core kernel, decode steps) and their partial results
 };
 
 // ------------------------------------------------------------------ plain kernel (any size, bf16 or float)
@@ -140,6 +142,21 @@ __device__ __forceinline__ void ldsm_x2_t(uint32_t& r0, uint32_t& r1, const void
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(smem_u32(p)));
 }
 
+// the same with 32-bit shared-space addresses, so that unrolled offsets fold into the instructions
+__device__ __forceinline__ void ldsm_x4_a(uint32_t* r, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2_a(uint32_t& r0, uint32_t& r1, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x2_t_a(uint32_t& r0, uint32_t& r1, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void cp_async_16_a(uint32_t dst, const void* gsrc, bool ok) {
+  const int bytes = ok ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst), "l"(gsrc), "r"(bytes) : "memory");
+}
+
 struct LatentMmaSmem {
   int q_off, k_off, s_off, p_off, st_off, total, ldk;   // byte offsets; ldk = padded row length in elements
 };
@@ -156,7 +173,7 @@ static LatentMmaSmem latent_mma_smem(int r, int dr) {
   return m;
 }
 
-template <int NW, int NT>
+template <int NW, int NT, int KSMAX>
 __global__ void __launch_bounds__(NW * 32)
 latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -168,7 +185,7 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
   float* row_l = row_m + 16;
   float* row_alpha = row_l + 16;
   int* row_pos = reinterpret_cast<int*>(row_alpha + 16);
-  constexpr int THREADS = NW * 32, LDP = LM_KT + 8, SN = LM_KT / 8 / NW;      // SN: score n-tiles per warp
+  constexpr int LDP = LM_KT + 8, SN = LM_KT / 8 / NW;      // SN: score n-tiles per warp
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int ldk = sm.ldk, dkp = ldk - 8, Dk = a.r + a.dr;
   const int b = blockIdx.y;
@@ -184,62 +201,121 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
   const int32_t* bt = a.block_tables + b * a.bt_stride;
   const int j_lo = a.window > 0 ? max(0, pos_first - a.window + 1) : 0;
   const int n_tiles = (pos_last - j_lo) / LM_KT + 1;
+  // with splits > 1, CTA z of a query tile takes the z-th run of key tiles and leaves (O, m, l) for the merge kernel
+  const int tps = (n_tiles + a.splits - 1) / a.splits;
+  const int t_begin = blockIdx.z * tps, t_end = min(n_tiles, t_begin + tps);
 
   // a warp copies whole rows: the page lookup is once per key and uniform over the warp, the lanes stride over the
   // row's 16-byte chunks; keys past the last query and the padding chunk are zero-filled
-  auto load_tile = [&](int t, int stage) {
-    __nv_bfloat16* dst = ks + static_cast<size_t>(stage) * LM_KT * ldk;
-    const int cpr = dkp / 8, real = Dk / 8;
-    // lane i looks up the i-th key of this warp: all the table reads of a tile are in flight together
-    long long my = -1;
-    if (lane < LM_KT / NW) {
+  // lane i looks up the i-th key of this warp's share of a tile; the lookup runs one tile ahead of the copies, so that
+  // its latency is never waited for
+  auto lookup = [&](int t) -> long long {
+    long long off = -1;
+    if (lane < LM_KT / NW && t < t_end) {
       const int j = j_lo + t * LM_KT + warp + lane * NW;
-      if (j <= pos_last) my = (static_cast<long long>(bt[j / a.page]) * a.page + j % a.page) * Dk;
+      if (j <= pos_last) off = (static_cast<long long>(bt[j / a.page]) * a.page + j % a.page) * Dk;
     }
+    return off;
+  };
+  const uint32_t ks_u = smem_u32(ks), ps_u = smem_u32(ps);
+  auto load_tile = [&](long long my, int stage) {
+    const uint32_t dst = ks_u + static_cast<uint32_t>(stage * LM_KT * ldk + warp * ldk + lane * 8) * 2u;
+    const int cpr = dkp / 8, real = Dk / 8;
 #pragma unroll
     for (int i = 0; i < LM_KT / NW; ++i) {
       const long long off = __shfl_sync(0xffffffffu, my, i);
       const bool in = off >= 0;
-      const __nv_bfloat16* src = cache + (in ? off : 0);
-      __nv_bfloat16* drow = dst + (warp + i * NW) * ldk;
-      for (int ch = lane; ch < cpr; ch += 32) cp_async_16(drow + ch * 8, src + ch * 8, in && ch < real);
+      const __nv_bfloat16* src = cache + (in ? off : 0) + lane * 8;
+      uint32_t d = dst + static_cast<uint32_t>(i * NW * ldk) * 2u;
+      for (int ch = lane; ch < cpr; ch += 32, d += 512u, src += 256) cp_async_16_a(d, src, in && ch < real);
     }
     cp_async_commit();
   };
-  load_tile(0, 0);
+  long long slots_next = lookup(t_begin);
+  if (t_begin < t_end) {
+    load_tile(slots_next, 0);
+    slots_next = lookup(t_begin + 1);
+  }
 
   // ---- the 16 query rows: [ql | rotate(qr)] as bf16, zero rows where the tile has no token or head
   if (tid < 16) {
     const int tl = tid / hpc, h = hb * 16 + tid % hpc;
     const bool ok = tl < n_tok && h < a.H;
     row_pos[tid] = ok ? pos_first + tl : -1;
-    row_m[tid] = ok ? a.sink[h] : 0.f;
-    row_l[tid] = 1.0f;
+    // the sink counts once: the first split starts from it (m = sink, l = exp(sink - m) = 1), the others from nothing
+    row_m[tid] = ok && blockIdx.z == 0 ? a.sink[h] : -1.0e30f;
+    row_l[tid] = blockIdx.z == 0 ? 1.0f : 0.f;
   }
-  for (int row = warp; row < 16; row += NW) {
-    const int tl = row / hpc, h = hb * 16 + row % hpc;
-    const bool ok = tl < n_tok && h < a.H;
-    const int tok = start + tl0 + tl;
-    const __nv_bfloat16* ql = static_cast<const __nv_bfloat16*>(a.ql) + tok * a.ql_tok + h * a.ql_head;
-    const __nv_bfloat16* qr = static_cast<const __nv_bfloat16*>(a.qr) + tok * a.qr_tok + h * a.qr_head;
-    for (int c0 = lane * 2; c0 < dkp; c0 += 64) {
-      float v0 = 0.f, v1 = 0.f;
-      if (ok && c0 < a.r) {
-        v0 = __bfloat162float(ql[c0]);
-        v1 = __bfloat162float(ql[c0 + 1]);
-      } else if (ok && c0 < Dk) {
-        const int d = c0 - a.r;
-        const float u = __bfloat162float(qr[d]), w = __bfloat162float(qr[d + 1]);
-        if (d + 1 < a.rot_dims) {
-          float sn, cs;
-          sincosf(static_cast<float>(pos_first + tl) * a.freq[d / 2], &sn, &cs);
-          sn *= a.rot_mult; cs *= a.rot_mult;
-          v0 = u * cs - w * sn;
-          v1 = w * cs + u * sn;
-        } else { v0 = u; v1 = w; }
+  {
+    // a warp stages rows warp, warp + NW, ..: first every load of its rows is issued (16 bytes of ql per lane and step,
+    // one pair of qr per lane), then the rows are written, so one round trip to memory covers them all
+    constexpr int ROWS = 16 / NW, QV = 4;                                  // QV steps of 32 x 8 numbers: latents up to 1024
+    const bool vec = a.ql_vec;
+    uint4 qv[ROWS][QV];
+    float2 rv[ROWS][2];
+#pragma unroll
+    for (int k = 0; k < ROWS; ++k) {
+      const int row = warp + k * NW;
+      const int tl = row / hpc, h = hb * 16 + row % hpc;
+      const bool ok = tl < n_tok && h < a.H;
+      const int tok = start + tl0 + tl;
+      const __nv_bfloat16* ql = static_cast<const __nv_bfloat16*>(a.ql) + tok * a.ql_tok + h * a.ql_head;
+      const __nv_bfloat16* qr = static_cast<const __nv_bfloat16*>(a.qr) + tok * a.qr_tok + h * a.qr_head;
+#pragma unroll
+      for (int v = 0; v < QV; ++v) {
+        const int c = (v * 32 + lane) * 8;
+        qv[k][v] = make_uint4(0u, 0u, 0u, 0u);
+        if (ok && c < a.r) {
+          if (vec) qv[k][v] = *reinterpret_cast<const uint4*>(ql + c);
+          else {
+            const unsigned short* q16 = reinterpret_cast<const unsigned short*>(ql + c);
+            qv[k][v] = make_uint4(q16[0] | (q16[1] << 16), q16[2] | (q16[3] << 16), q16[4] | (q16[5] << 16), q16[6] | (q16[7] << 16));
+          }
+        }
       }
-      *reinterpret_cast<__nv_bfloat162*>(qs + row * ldk + c0) = __floats2bfloat162_rn(v0, v1);
+#pragma unroll
+      for (int v = 0; v < 2; ++v) {
+        const int d = (v * 32 + lane) * 2;
+        rv[k][v] = make_float2(0.f, 0.f);
+        if (ok && d < a.dr) rv[k][v] = make_float2(__bfloat162float(qr[d]), __bfloat162float(qr[d + 1]));
+      }
     }
+#pragma unroll
+    for (int k = 0; k < ROWS; ++k) {
+      const int row = warp + k * NW;
+      const int tl = row / hpc;
+#pragma unroll
+      for (int v = 0; v < QV; ++v) {
+        const int c = (v * 32 + lane) * 8;
+        if (c < a.r) *reinterpret_cast<uint4*>(qs + row * ldk + c) = qv[k][v];
+      }
+#pragma unroll
+      for (int v = 0; v < 2; ++v) {
+        const int d = (v * 32 + lane) * 2;
+        if (d < dkp - a.r) {                                               // the rotary part and the zero padding after it
+          float v0 = rv[k][v].x, v1 = rv[k][v].y;
+          if (d + 1 < a.rot_dims) {
+            float sn, cs;
+            sincosf(static_cast<float>(pos_first + tl) * a.freq[d / 2], &sn, &cs);
+            sn *= a.rot_mult; cs *= a.rot_mult;
+            const float u = v0, w = v1;
+            v0 = u * cs - w * sn;
+            v1 = w * cs + u * sn;
+          }
+          *reinterpret_cast<__nv_bfloat162*>(qs + row * ldk + a.r + d) = __floats2bfloat162_rn(v0, v1);
+        }
+      }
+    }
+  }
+
+  // every warp keeps the whole query tile as MMA fragments in registers (KSMAX k-steps of 16): the score product then
+  // reads only key rows from shared memory, whose bandwidth is what bounds it otherwise
+  __syncthreads();
+  uint32_t qf[KSMAX][4];
+#pragma unroll
+  for (int u = 0; u < KSMAX; ++u) {
+    if (u * 16 < dkp) ldsm_x4_a(qf[u], smem_u32(qs) + static_cast<uint32_t>((lane & 15) * ldk + (lane >> 4) * 8) * 2u + u * 32u);
+    else qf[u][0] = qf[u][1] = qf[u][2] = qf[u][3] = 0u;
   }
 
   float acc[NT][4];
@@ -247,35 +323,41 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
   for (int i = 0; i < NT; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
   const int col0 = warp * NT * 8;                                   // this warp's columns of O
 
-  for (int t = 0; t < n_tiles; ++t) {
-    const int stage = t & 1;
-    if (t + 1 < n_tiles) { load_tile(t + 1, stage ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
+  for (int t = t_begin; t < t_end; ++t) {
+    const int stage = (t - t_begin) & 1;
+    if (t + 1 < t_end) {
+      load_tile(slots_next, stage ^ 1);
+      slots_next = lookup(t + 2);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
     __syncthreads();
-    const __nv_bfloat16* kt = ks + static_cast<size_t>(stage) * LM_KT * ldk;
     // ---- S = Q K^T for this warp's keys
     float sc[SN][2][4];                          // two accumulators per n-tile: alternate k-steps do not wait on each other
 #pragma unroll
     for (int i = 0; i < SN; ++i)
 #pragma unroll
       for (int e = 0; e < 4; ++e) sc[i][0][e] = sc[i][1][e] = 0.f;
-    const __nv_bfloat16* q_lane = qs + (lane & 15) * ldk + (lane >> 4) * 8;
-    const __nv_bfloat16* k_lane = kt + (warp * SN * 8 + (lane & 7)) * ldk + ((lane >> 3) & 1) * 8;
-    for (int k0 = 0; k0 < dkp; k0 += 64) {       // the loads of four k-steps are issued before their products
-      uint32_t af[4][4], bf[4][SN][2];
+    const uint32_t kt_u = ks_u + static_cast<uint32_t>(stage * LM_KT * ldk) * 2u;
+    const uint32_t k_lane = kt_u + static_cast<uint32_t>((warp * SN * 8 + (lane & 7)) * ldk + ((lane >> 3) & 1) * 8) * 2u;
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int k = k0 + 16 * u;
-        if (k < dkp) {
-          ldsm_x4(af[u][0], af[u][1], af[u][2], af[u][3], q_lane + k);
+    for (int u0 = 0; u0 < KSMAX; u0 += 4) {      // the key fragments of four k-steps are in flight before their products
+      if (u0 * 16 < dkp) {
+        uint32_t bf[4][SN][2];
 #pragma unroll
-          for (int i = 0; i < SN; ++i) ldsm_x2(bf[u][i][0], bf[u][i][1], k_lane + i * 8 * ldk + k);
+        for (int u = 0; u < 4; ++u) {
+          if ((u0 + u) * 16 < dkp) {
+#pragma unroll
+            for (int i = 0; i < SN; ++i) ldsm_x2_a(bf[u][i][0], bf[u][i][1], k_lane + static_cast<uint32_t>(i * 8 * ldk) * 2u + (u0 + u) * 32u);
+          }
         }
-      }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        if (k0 + 16 * u < dkp) {
+        for (int u = 0; u < 4; ++u) {
+          if ((u0 + u) * 16 < dkp) {
 #pragma unroll
-          for (int i = 0; i < SN; ++i) mma_bf16_16816(sc[i][u & 1], af[u], bf[u][i][0], bf[u][i][1]);
+            for (int i = 0; i < SN; ++i) mma_bf16_16816(sc[i][u & 1], qf[u0 + u], bf[u][i][0], bf[u][i][1]);
+          }
         }
       }
     }
@@ -329,19 +411,42 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
       const float a0 = row_alpha[lane >> 2], a1 = row_alpha[(lane >> 2) + 8];
 #pragma unroll
       for (int i = 0; i < NT; ++i) { acc[i][0] *= a0; acc[i][1] *= a0; acc[i][2] *= a1; acc[i][3] *= a1; }
+      const uint32_t p_lane = ps_u + static_cast<uint32_t>((lane & 15) * LDP + (lane >> 4) * 8) * 2u;
+      const uint32_t v_lane = kt_u + static_cast<uint32_t>((lane & 15) * ldk + col0) * 2u;
+      const uint32_t v_step = static_cast<uint32_t>(16 * ldk) * 2u;
 #pragma unroll
-      for (int kk = 0; kk < LM_KT; kk += 16) {
+      for (int kk = 0; kk < LM_KT / 16; ++kk) {
         uint32_t pf[4];
-        ldsm_x4(pf[0], pf[1], pf[2], pf[3], ps + (lane & 15) * LDP + kk + (lane >> 4) * 8);
+        ldsm_x4_a(pf, p_lane + kk * 32u);
+        uint32_t vb[NT][2];
 #pragma unroll
-        for (int i = 0; i < NT; ++i) {
-          uint32_t b0, b1;
-          ldsm_x2_t(b0, b1, kt + (kk + (lane & 15)) * ldk + col0 + i * 8);
-          mma_bf16_16816(acc[i], pf, b0, b1);
-        }
+        for (int i = 0; i < NT; ++i) ldsm_x2_t_a(vb[i][0], vb[i][1], v_lane + kk * v_step + i * 16u);
+#pragma unroll
+        for (int i = 0; i < NT; ++i) mma_bf16_16816(acc[i], pf, vb[i][0], vb[i][1]);
       }
     }
     __syncthreads();
+  }
+  if (a.splits > 1) {
+    // ---- partial result of this key range: un-normalised O, then m and l, per row
+    __syncthreads();                               // row_m / row_l of the last tile (and of a CTA with no tile at all)
+    float* wrow = a.ws + ((static_cast<size_t>(b) * gridDim.x + blockIdx.x) * a.splits + blockIdx.z) * 16 * (a.r + 2);
+    const int r0 = lane >> 2;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      float* w = wrow + static_cast<size_t>(r0 + 8 * half) * (a.r + 2);
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        const int c = col0 + i * 8 + (lane & 3) * 2;
+        w[c] = acc[i][2 * half];
+        w[c + 1] = acc[i][2 * half + 1];
+      }
+    }
+    if (tid < 16) {
+      wrow[static_cast<size_t>(tid) * (a.r + 2) + a.r] = row_m[tid];
+      wrow[static_cast<size_t>(tid) * (a.r + 2) + a.r + 1] = row_l[tid];
+    }
+    return;
   }
   // ---- out = O / l
   {
@@ -363,9 +468,35 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
   }
 }
 
-template <int NW, int NT>
+// Merge of the key ranges of one query row: out = sum_z O_z e^(m_z - M) / sum_z l_z e^(m_z - M), M = max_z m_z.
+// grid (query tiles, sequences, 16 rows).
+__global__ void __launch_bounds__(128)
+latent_attn_merge_kernel(const LatentAttnArgs a) {
+  const int b = blockIdx.y, row = blockIdx.z;
+  const int len = a.seq_len[b];
+  const int hpc = min(a.H, 16), hblocks = (a.H + 15) / 16, G = 16 / hpc;
+  const int tile = blockIdx.x / hblocks, hb = blockIdx.x % hblocks;
+  const int tl0 = tile * G;
+  const int tl = row / hpc, h = hb * 16 + row % hpc;
+  if (tl0 + tl >= len || tl >= G || h >= a.H) return;
+  const int stride = 16 * (a.r + 2);
+  const float* w = a.ws + (static_cast<size_t>(b) * gridDim.x + blockIdx.x) * a.splits * stride + static_cast<size_t>(row) * (a.r + 2);
+  float M = -1.0e30f;
+  for (int z = 0; z < a.splits; ++z) M = fmaxf(M, w[z * stride + a.r]);
+  float L = 0.f;
+  for (int z = 0; z < a.splits; ++z) L += w[z * stride + a.r + 1] * expf(w[z * stride + a.r] - M);
+  const float inv = 1.0f / L;
+  __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(a.out) + (a.seq_start[b] + tl0 + tl) * a.o_tok + h * a.o_head;
+  for (int c = threadIdx.x; c < a.r; c += blockDim.x) {
+    float o = 0.f;
+    for (int z = 0; z < a.splits; ++z) o += w[z * stride + c] * expf(w[z * stride + a.r] - M);
+    orow[c] = __float2bfloat16_rn(o * inv);
+  }
+}
+
+template <int NW, int NT, int KSMAX>
 static cudaError_t launch_latent_mma(const LatentAttnArgs& a, const LatentMmaSmem& sm, dim3 grid, cudaStream_t st) {
-  auto kern = latent_attn_mma_kernel<NW, NT>;
+  auto kern = latent_attn_mma_kernel<NW, NT, KSMAX>;
   if (sm.total > 48 * 1024) {
     static bool raised = false;                  // one attribute per kernel instance: raise it to the card's limit once
     if (!raised) {
@@ -386,17 +517,19 @@ static bool latent_mma_fits(const LatentAttnArgs& a, int* nw, int* nt) {
   if (tiles % 8 == 0 && tiles / 8 <= 8) { *nw = 8; *nt = tiles / 8; }
   else if (tiles % 4 == 0 && tiles / 4 <= 8) { *nw = 4; *nt = tiles / 4; }
   else return false;
-  if (latent_mma_smem(a.r, a.dr).total > 220 * 1024) return false;
+  if (latent_mma_smem(a.r, a.dr).total > 220 * 1024 || (a.r + a.dr + 15) / 16 > 40) return false;
   if (reinterpret_cast<uintptr_t>(a.cache) % 16) return false;
-  if (a.rot_dims % 2 || (a.dr % 2)) return false;
+  if (a.rot_dims % 2 || a.r > 1024 || a.dr > 120) return false;
   return true;
 }
 
 static cudaError_t run_latent_mma(const LatentAttnArgs& a, int nw, int nt, cudaStream_t st) {
   const LatentMmaSmem sm = latent_mma_smem(a.r, a.dr);
   const int hpc = a.H < 16 ? a.H : 16, hblocks = (a.H + 15) / 16, G = 16 / hpc;
-  const dim3 grid(static_cast<unsigned>((a.max_new + G - 1) / G) * hblocks, a.n_seqs);
-#define LM_GO(NW, NT) return launch_latent_mma<NW, NT>(a, sm, grid, st)
+  const dim3 grid(static_cast<unsigned>((a.max_new + G - 1) / G) * hblocks, a.n_seqs, a.splits);
+  // the query fragments a warp keeps: 8 k-steps cover keys up to 128 numbers wide, 40 up to 640
+  const bool small = (a.r + a.dr + 15) / 16 <= 8;
+#define LM_GO(NW, NT) return small ? launch_latent_mma<NW, NT, 8>(a, sm, grid, st) : launch_latent_mma<NW, NT, 40>(a, sm, grid, st)
 #define LM_NT(NW) switch (nt) { case 1: LM_GO(NW, 1); case 2: LM_GO(NW, 2); case 3: LM_GO(NW, 3); case 4: LM_GO(NW, 4); \
                                 case 5: LM_GO(NW, 5); case 6: LM_GO(NW, 6); case 7: LM_GO(NW, 7); case 8: LM_GO(NW, 8); }
   if (nw == 8) { LM_NT(8) } else { LM_NT(4) }
@@ -413,7 +546,7 @@ extern "C" int b2tts_latent_attn(const void* ql, int64_t ql_tok, int64_t ql_head
                                  float rot_mult, int rot_dims, const int32_t* seq_start, const int32_t* seq_pos0,
                                  const int32_t* seq_len, const int32_t* block_tables, int64_t bt_stride, int n_seqs, int max_new,
                                  int heads, int kv_rank, int rot_dim, int page, int window, float scale, int dtype, int path,
-                                 void* stream) {
+                                 int splits, float* ws, void* stream) {
   using namespace b2;
   using namespace b2::lat;
   B2_REQUIRE(n_seqs >= 0 && max_new >= 0 && heads > 0 && kv_rank > 0 && rot_dim >= 0 && page > 0 && window >= 0, B2TTS_EINVAL,
@@ -426,14 +559,22 @@ extern "C" int b2tts_latent_attn(const void* ql, int64_t ql_tok, int64_t ql_head
              (rot_dims == 0 || freq), B2TTS_EINVAL, "latent_attn: null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   LatentAttnArgs a{ql, ql_tok, ql_head, qr, qr_tok, qr_head, cache, out, o_tok, o_head, sink, freq, rot_mult, rot_dims,
-                   seq_start, seq_pos0, seq_len, block_tables, bt_stride, n_seqs, max_new, heads, kv_rank, rot_dim, page, window, scale};
+                   seq_start, seq_pos0, seq_len, block_tables, bt_stride, n_seqs, max_new, heads, kv_rank, rot_dim, page, window, scale, 0, 1, nullptr};
   int nw = 0, nt = 0;
   const bool fits = dtype == B2TTS_DTYPE_BF16 && latent_mma_fits(a, &nw, &nt);
   B2_REQUIRE(path != 2 || fits, B2TTS_EUNSUPPORTED, "latent_attn: the tensor-core kernel does not take kv_rank %d, rot_dim %d", kv_rank, rot_dim);
   if (fits && path != 1) {
+    a.ql_vec = reinterpret_cast<uintptr_t>(ql) % 16 == 0 && ql_tok % 8 == 0 && ql_head % 8 == 0;
+    a.splits = (splits > 1 && ws != nullptr) ? splits : 1;
+    a.ws = ws;
     cudaError_t e = run_latent_mma(a, nw, nt, st);
     if (e != cudaSuccess) return cuda_fail(e, "latent_attn (tensor)");
     B2_CHECK_LAUNCH("latent_attn (tensor)");
+    if (a.splits > 1) {
+      const int hpc = heads < 16 ? heads : 16, G = 16 / hpc;
+      latent_attn_merge_kernel<<<dim3(static_cast<unsigned>((max_new + G - 1) / G) * ((heads + 15) / 16), n_seqs, 16), 128, 0, st>>>(a);
+      B2_CHECK_LAUNCH("latent_attn (merge)");
+    }
     return B2TTS_OK;
   }
   const size_t smem = static_cast<size_t>(LA_WARPS) * (kv_rank + rot_dim) * sizeof(float);
@@ -443,4 +584,17 @@ extern "C" int b2tts_latent_attn(const void* ql, int64_t ql_tok, int64_t ql_head
   else latent_attn_kernel<float><<<grid, LA_WARPS * 32, smem, st>>>(a);
   B2_CHECK_LAUNCH("latent_attn");
   return B2TTS_OK;
+}
+
+/* How many key ranges a decode step's query tiles are cut into so that the tensor-core kernel fills the GPU (1 = no cut),
+ * and the float workspace that many need. */
+extern "C" int b2tts_latent_attn_splits(int n_seqs, int max_new, int heads) {
+  if (max_new != 1 || n_seqs <= 0) return 1;
+  const int ctas = n_seqs * ((heads + 15) / 16);
+  int s = 148 / ctas;
+  return s < 1 ? 1 : (s > 8 ? 8 : s);
+}
+extern "C" size_t b2tts_latent_attn_workspace_floats(int n_seqs, int max_new, int heads, int kv_rank, int splits) {
+  const int hpc = heads < 16 ? heads : 16, G = 16 / hpc;
+  return static_cast<size_t>(n_seqs) * ((max_new + G - 1) / G) * ((heads + 15) / 16) * splits * 16 * (kv_rank + 2);
 }

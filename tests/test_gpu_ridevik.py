@@ -149,7 +149,8 @@ def test_latent_preparation_norms_rotation_and_cache_rows(nat, q_rank, kv_rank, 
     assert rel(rows[:14, kv_rank:], kr_ref[:14]) < 1e-5
 
 
-def _attn_case(nat, H, r, dr, window, page, seqs, dtype=torch.float32, spike=None, sink_big=None, seed=0, path=0, rot_dims=None):
+def _attn_case(nat, H, r, dr, window, page, seqs, dtype=torch.float32, spike=None, sink_big=None, seed=0, path=0, rot_dims=None,
+               splits=None):
     """seqs: [(cached tokens, new tokens)].  Fills the cache with the sequences' rows, runs the kernel for the new
     tokens, compares with the plain implementation over the whole sequence.  ``spike`` = (sequence, key position): that
     key's score exceeds every other by a wide margin for every query.  ``sink_big``: head whose sink swallows the softmax."""
@@ -191,7 +192,7 @@ def _attn_case(nat, H, r, dr, window, page, seqs, dtype=torch.float32, spike=Non
     qr = torch.cat([QR[s][c:] for s, (c, n) in enumerate(seqs)]).contiguous().to(DEV)                        # [n, H, dr]
     out = torch.full((H, n_new, r), 7.0, dtype=dtype, device=DEV)
     nat.latent_attn(ql, (r, n_new * r), qr, (H * dr, dr), cache, out, (r, n_new * r), sink.to(DEV), rot.freq, 1.0, rot_dims, lay,
-                    H, r, dr, page, window, scale, path)
+                    H, r, dr, page, window, scale, path, splits_override=splits)
     got = out.transpose(0, 1).cpu()
     o = 0
     worst = 0.0
@@ -225,6 +226,20 @@ def test_tensor_core_latent_attention_against_plain_model_and_plain_kernel(nat, 
         e_t = _attn_case(nat, H, r, dr, window, page, seqs, dtype=torch.bfloat16, seed=H + window, path=nat.LATENT_ATTN_TENSOR, rot_dims=rd)
         e_p = _attn_case(nat, H, r, dr, window, page, seqs, dtype=torch.bfloat16, seed=H + window, path=nat.LATENT_ATTN_PLAIN, rot_dims=rd)
         assert e_t < 2e-2 and e_p < 2e-2, (e_t, e_p)
+
+
+@pytest.mark.parametrize("H,r,dr", [(8, 64, 32), (4, 96, 16), (20, 64, 8)])
+@pytest.mark.parametrize("window", [0, 70, 300])
+def test_decode_steps_whose_keys_are_cut_into_ranges_and_merged(nat, H, r, dr, window):
+    """A decode step on the tensor-core kernel with each sequence's keys cut into 2, 3 or 8 ranges (more ranges than some
+    sequences have key tiles: empty ranges; the sink must count once), also with a spiked key in the last or first range."""
+    seqs = [(400, 1), (63, 1), (0, 1), (64, 1), (129, 1), (777, 1)]
+    for splits in (None, 2, 3, 8):
+        assert _attn_case(nat, H, r, dr, window, 64, seqs, dtype=torch.bfloat16, seed=H, path=nat.LATENT_ATTN_TENSOR, splits=splits) < 2e-2
+    for sp in ((0, 399), (0, 5), (5, 500), (5, 776)):
+        assert _attn_case(nat, H, r, dr, window, 16, seqs, dtype=torch.bfloat16, seed=H, path=nat.LATENT_ATTN_TENSOR, splits=3, spike=sp) < 2e-2
+    assert _attn_case(nat, H, r, dr, window, 16, [(100, 9), (300, 40)], dtype=torch.bfloat16, seed=1, path=nat.LATENT_ATTN_TENSOR, splits=2) < 2e-2
+    assert _attn_case(nat, H, r, dr, 0, 16, seqs, dtype=torch.bfloat16, seed=2, path=nat.LATENT_ATTN_TENSOR, splits=4, sink_big=1) < 2e-2
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
