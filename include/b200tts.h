@@ -489,7 +489,8 @@ B2TTS_API int b2tts_latent_prep(const void* u, int64_t ldu, int q_off, int kv_of
 /* Multi-query softmax attention over cached rows [c | kr] with a sink in the denominator; see csrc/latent_attn.cu.
  * ql: absorbed queries (element (t, h, :) at ql + t * ql_tok + h * ql_head, kv_rank numbers), qr: rotary query parts, not yet
  * turned (rot_dim numbers), out: weighted latent sums (kv_rank numbers), strides in elements.  window 0 = every earlier key.
- * path 0 = choose, 1 = the plain kernel, 2 = the tensor-core kernel (bf16; fails if the sizes do not fit it). */
+ * path 0 = choose, 1 = the plain kernel, 2 = the tensor-core kernel with two key stages (bf16; fails if the sizes do not
+ * fit it), 3 = the tensor-core kernel with one key stage and two CTAs per SM. */
 B2TTS_API int b2tts_latent_attn(const void* ql, int64_t ql_tok, int64_t ql_head, const void* qr, int64_t qr_tok, int64_t qr_head,
                                 const void* cache, void* out, int64_t o_tok, int64_t o_head, const float* sink, const float* freq,
                                 float rot_mult, int rot_dims, const int32_t* seq_start, const int32_t* seq_pos0,

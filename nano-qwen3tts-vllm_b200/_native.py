@@ -815,7 +815,7 @@ def latent_prep(u, q_off, kv_off, cq, q_norm_w, kv_norm_w, freq, rot_mult, lay, 
                                      lay.n_tokens, q_rank, kv_rank, rot_dim, rot_dims, eps, dt, _stream()), "latent_prep")
 
 
-LATENT_ATTN_AUTO, LATENT_ATTN_PLAIN, LATENT_ATTN_TENSOR = 0, 1, 2
+LATENT_ATTN_AUTO, LATENT_ATTN_PLAIN, LATENT_ATTN_TENSOR, LATENT_ATTN_TENSOR_SHARED = 0, 1, 2, 3
 
 
 def latent_attn(ql, ql_strides, qr, qr_strides, cache, out, out_strides, sink, freq, rot_mult, rot_dims, lay, heads, kv_rank,

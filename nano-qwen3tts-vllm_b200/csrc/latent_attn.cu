@@ -160,21 +160,23 @@ __device__ __forceinline__ void cp_async_16_a(uint32_t dst, const void* gsrc, bo
 struct LatentMmaSmem {
   int q_off, k_off, s_off, p_off, st_off, total, ldk;   // byte offsets; ldk = padded row length in elements
 };
-static LatentMmaSmem latent_mma_smem(int r, int dr) {
+static LatentMmaSmem latent_mma_smem(int r, int dr, int stages = 2) {
   LatentMmaSmem m;
   const int dkp = (r + dr + 15) / 16 * 16;
   m.ldk = dkp + 8;
   m.q_off = 0;
   m.k_off = 16 * m.ldk * 2;
-  m.s_off = m.k_off + 2 * LM_KT * m.ldk * 2;
+  m.s_off = m.k_off + stages * LM_KT * m.ldk * 2;
   m.p_off = m.s_off + 16 * LM_KT * 4;
   m.st_off = m.p_off + 16 * (LM_KT + 8) * 2;
   m.total = m.st_off + 16 * 4 * 4;
   return m;
 }
 
+// KSMAX > 0: two key stages and the query fragments in registers (one CTA per SM).  KSMAX == 0: one key stage, query
+// fragments re-read from shared memory, half the registers - two CTAs share an SM and cover each other's waits.
 template <int NW, int NT, int KSMAX>
-__global__ void __launch_bounds__(NW * 32)
+__global__ void __launch_bounds__(NW * 32, KSMAX == 0 ? 2 : 1)
 latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw + sm.q_off);
@@ -311,12 +313,16 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
   // every warp keeps the whole query tile as MMA fragments in registers (KSMAX k-steps of 16): the score product then
   // reads only key rows from shared memory, whose bandwidth is what bounds it otherwise
   __syncthreads();
-  uint32_t qf[KSMAX][4];
+  constexpr bool QREG = KSMAX > 0;
+  uint32_t qf[QREG ? KSMAX : 1][4];
+  if (QREG) {
 #pragma unroll
-  for (int u = 0; u < KSMAX; ++u) {
-    if (u * 16 < dkp) ldsm_x4_a(qf[u], smem_u32(qs) + static_cast<uint32_t>((lane & 15) * ldk + (lane >> 4) * 8) * 2u + u * 32u);
-    else qf[u][0] = qf[u][1] = qf[u][2] = qf[u][3] = 0u;
+    for (int u = 0; u < KSMAX; ++u) {
+      if (u * 16 < dkp) ldsm_x4_a(qf[u], smem_u32(qs) + static_cast<uint32_t>((lane & 15) * ldk + (lane >> 4) * 8) * 2u + u * 32u);
+      else qf[u][0] = qf[u][1] = qf[u][2] = qf[u][3] = 0u;
+    }
   }
+  const uint32_t q_lane = smem_u32(qs) + static_cast<uint32_t>((lane & 15) * ldk + (lane >> 4) * 8) * 2u;
 
   float acc[NT][4];
 #pragma unroll
@@ -324,8 +330,8 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
   const int col0 = warp * NT * 8;                                   // this warp's columns of O
 
   for (int t = t_begin; t < t_end; ++t) {
-    const int stage = (t - t_begin) & 1;
-    if (t + 1 < t_end) {
+    const int stage = QREG ? (t - t_begin) & 1 : 0;
+    if (QREG && t + 1 < t_end) {
       load_tile(slots_next, stage ^ 1);
       slots_next = lookup(t + 2);
       cp_async_wait<1>();
@@ -341,22 +347,43 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
       for (int e = 0; e < 4; ++e) sc[i][0][e] = sc[i][1][e] = 0.f;
     const uint32_t kt_u = ks_u + static_cast<uint32_t>(stage * LM_KT * ldk) * 2u;
     const uint32_t k_lane = kt_u + static_cast<uint32_t>((warp * SN * 8 + (lane & 7)) * ldk + ((lane >> 3) & 1) * 8) * 2u;
+    if (QREG) {
 #pragma unroll
-    for (int u0 = 0; u0 < KSMAX; u0 += 4) {      // the key fragments of four k-steps are in flight before their products
-      if (u0 * 16 < dkp) {
-        uint32_t bf[4][SN][2];
+      for (int u0 = 0; u0 < KSMAX; u0 += 4) {    // the key fragments of four k-steps are in flight before their products
+        if (u0 * 16 < dkp) {
+          uint32_t bf[4][SN][2];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if ((u0 + u) * 16 < dkp) {
+#pragma unroll
+              for (int i = 0; i < SN; ++i) ldsm_x2_a(bf[u][i][0], bf[u][i][1], k_lane + static_cast<uint32_t>(i * 8 * ldk) * 2u + (u0 + u) * 32u);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if ((u0 + u) * 16 < dkp) {
+#pragma unroll
+              for (int i = 0; i < SN; ++i) mma_bf16_16816(sc[i][u & 1], qf[QREG ? u0 + u : 0], bf[u][i][0], bf[u][i][1]);
+            }
+          }
+        }
+      }
+    } else {
+      for (int k0 = 0; k0 < dkp; k0 += 64) {
+        uint32_t af[4][4], bf[4][SN][2];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          if ((u0 + u) * 16 < dkp) {
+          if (k0 + 16 * u < dkp) {
+            ldsm_x4_a(af[u], q_lane + (k0 + 16 * u) * 2u);
 #pragma unroll
-            for (int i = 0; i < SN; ++i) ldsm_x2_a(bf[u][i][0], bf[u][i][1], k_lane + static_cast<uint32_t>(i * 8 * ldk) * 2u + (u0 + u) * 32u);
+            for (int i = 0; i < SN; ++i) ldsm_x2_a(bf[u][i][0], bf[u][i][1], k_lane + static_cast<uint32_t>(i * 8 * ldk) * 2u + (k0 + 16 * u) * 2u);
           }
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          if ((u0 + u) * 16 < dkp) {
+          if (k0 + 16 * u < dkp) {
 #pragma unroll
-            for (int i = 0; i < SN; ++i) mma_bf16_16816(sc[i][u & 1], qf[u0 + u], bf[u][i][0], bf[u][i][1]);
+            for (int i = 0; i < SN; ++i) mma_bf16_16816(sc[i][u & 1], af[u], bf[u][i][0], bf[u][i][1]);
           }
         }
       }
@@ -426,6 +453,10 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
       }
     }
     __syncthreads();
+    if (!QREG && t + 1 < t_end) {                 // one stage: the next tile may only land once everyone is done with this one
+      load_tile(slots_next, 0);
+      slots_next = lookup(t + 2);
+    }
   }
   if (a.splits > 1) {
     // ---- partial result of this key range: un-normalised O, then m and l, per row
@@ -495,8 +526,9 @@ latent_attn_merge_kernel(const LatentAttnArgs a) {
 }
 
 template <int NW, int NT, int KSMAX>
-static cudaError_t launch_latent_mma(const LatentAttnArgs& a, const LatentMmaSmem& sm, dim3 grid, cudaStream_t st) {
+static cudaError_t launch_latent_mma(const LatentAttnArgs& a, const LatentMmaSmem& sm_in, dim3 grid, cudaStream_t st) {
   auto kern = latent_attn_mma_kernel<NW, NT, KSMAX>;
+  const LatentMmaSmem sm = KSMAX == 0 ? latent_mma_smem(a.r, a.dr, 1) : sm_in;
   if (sm.total > 48 * 1024) {
     static bool raised = false;                  // one attribute per kernel instance: raise it to the card's limit once
     if (!raised) {
@@ -523,13 +555,14 @@ static bool latent_mma_fits(const LatentAttnArgs& a, int* nw, int* nt) {
   return true;
 }
 
-static cudaError_t run_latent_mma(const LatentAttnArgs& a, int nw, int nt, cudaStream_t st) {
+static cudaError_t run_latent_mma(const LatentAttnArgs& a, int nw, int nt, bool shared_sm, cudaStream_t st) {
   const LatentMmaSmem sm = latent_mma_smem(a.r, a.dr);
   const int hpc = a.H < 16 ? a.H : 16, hblocks = (a.H + 15) / 16, G = 16 / hpc;
   const dim3 grid(static_cast<unsigned>((a.max_new + G - 1) / G) * hblocks, a.n_seqs, a.splits);
   // the query fragments a warp keeps: 8 k-steps cover keys up to 128 numbers wide, 40 up to 640
   const bool small = (a.r + a.dr + 15) / 16 <= 8;
-#define LM_GO(NW, NT) return small ? launch_latent_mma<NW, NT, 8>(a, sm, grid, st) : launch_latent_mma<NW, NT, 40>(a, sm, grid, st)
+#define LM_GO(NW, NT) return shared_sm ? launch_latent_mma<NW, NT, 0>(a, sm, grid, st) : small ? launch_latent_mma<NW, NT, 8>(a, sm, grid, st) \
+                                                                                                : launch_latent_mma<NW, NT, 40>(a, sm, grid, st)
 #define LM_NT(NW) switch (nt) { case 1: LM_GO(NW, 1); case 2: LM_GO(NW, 2); case 3: LM_GO(NW, 3); case 4: LM_GO(NW, 4); \
                                 case 5: LM_GO(NW, 5); case 6: LM_GO(NW, 6); case 7: LM_GO(NW, 7); case 8: LM_GO(NW, 8); }
   if (nw == 8) { LM_NT(8) } else { LM_NT(4) }
@@ -563,11 +596,15 @@ extern "C" int b2tts_latent_attn(const void* ql, int64_t ql_tok, int64_t ql_head
   int nw = 0, nt = 0;
   const bool fits = dtype == B2TTS_DTYPE_BF16 && latent_mma_fits(a, &nw, &nt);
   B2_REQUIRE(path != 2 || fits, B2TTS_EUNSUPPORTED, "latent_attn: the tensor-core kernel does not take kv_rank %d, rot_dim %d", kv_rank, rot_dim);
+  B2_REQUIRE(path != 3 || fits, B2TTS_EUNSUPPORTED, "latent_attn: the tensor-core kernel does not take kv_rank %d, rot_dim %d", kv_rank, rot_dim);
   if (fits && path != 1) {
     a.ql_vec = reinterpret_cast<uintptr_t>(ql) % 16 == 0 && ql_tok % 8 == 0 && ql_head % 8 == 0;
     a.splits = (splits > 1 && ws != nullptr) ? splits : 1;
     a.ws = ws;
-    cudaError_t e = run_latent_mma(a, nw, nt, st);
+    // prompt portions: many CTAs, so two small ones per SM cover each other's waits; a decode step has few CTAs, each
+    // of which hides its own loads behind a second key stage
+    const bool shared_sm = path == 3 || (path == 0 && max_new > 1);
+    cudaError_t e = run_latent_mma(a, nw, nt, shared_sm, st);
     if (e != cudaSuccess) return cuda_fail(e, "latent_attn (tensor)");
     B2_CHECK_LAUNCH("latent_attn (tensor)");
     if (a.splits > 1) {
