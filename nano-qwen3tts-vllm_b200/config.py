@@ -281,8 +281,9 @@ class RidevikConfig:
                 else:
                     raise ValueError(f"layer {i}: unknown feed-forward kind {f['kind']!r}")
             src = ld.get("weights_of")
-            if src is not None and not (0 <= int(src) < i and d["layers"][int(src)].get("weights_of") is None):
-                raise ValueError(f"layer {i}: weights_of {src} must name an earlier layer with tensors of its own")
+            if src is not None and not (0 <= int(src) < len(d["layers"]) and int(src) != i
+                                        and d["layers"][int(src)].get("weights_of") is None):
+                raise ValueError(f"layer {i}: weights_of {src} must name another layer with tensors of its own")
             layers.append(RidevikLayerSpec(ld["type"], mixer, mlp, None if src is None else int(src)))
         c = cls(architecture=d["architecture"], vocab=int(d["vocab"]), width=int(d["width"]),
                 embedding_scale=float(d["embedding"]["scale"]), norm_eps=float(d["norm"]["eps"]),

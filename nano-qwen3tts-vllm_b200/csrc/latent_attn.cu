@@ -24,6 +24,18 @@ template <typename T> __device__ __forceinline__ T a_from_f(float v);
 template <> __device__ __forceinline__ float a_from_f<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 a_from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+template <typename T> __device__ __forceinline__ float dot_chunk(const uint4& v, const float* q);
+template <> __device__ __forceinline__ float dot_chunk<float>(const uint4& v, const float* q) {
+  return __uint_as_float(v.x) * q[0] + __uint_as_float(v.y) * q[1] + __uint_as_float(v.z) * q[2] + __uint_as_float(v.w) * q[3];
+}
+template <> __device__ __forceinline__ float dot_chunk<__nv_bfloat16>(const uint4& v, const float* q) {
+  // a bf16 is the upper half of a float
+  return __uint_as_float(v.x << 16) * q[0] + __uint_as_float(v.x & 0xffff0000u) * q[1] +
+         __uint_as_float(v.y << 16) * q[2] + __uint_as_float(v.y & 0xffff0000u) * q[3] +
+         __uint_as_float(v.z << 16) * q[4] + __uint_as_float(v.z & 0xffff0000u) * q[5] +
+         __uint_as_float(v.w << 16) * q[6] + __uint_as_float(v.w & 0xffff0000u) * q[7];
+}
+
 struct LatentAttnArgs {
   const void* ql; int64_t ql_tok, ql_head;      // absorbed queries [.., r]
   const void* qr; int64_t qr_tok, qr_head;      // un-rotated rotary query parts [.., dr]
@@ -34,7 +46,7 @@ struct LatentAttnArgs {
   const int32_t *seq_start, *seq_pos0, *seq_len, *block_tables; int64_t bt_stride;
   int n_seqs, max_new, H, r, dr, page, window;
   float scale;
-  int ql_vec;                                    // ql rows can be read 16 bytes at a time
+  int ql_vec;                                    // tensor-core kernel: ql rows, plain kernel: cache rows can be read 16 bytes at a time
   int splits; float* ws;                         // key ranges per query tile (tensor-core kernel, decode steps) and their partial results
 };
 
@@ -93,7 +105,13 @@ latent_attn_kernel(const LatentAttnArgs a) {
       slot = static_cast<size_t>(bt[j / a.page]) * a.page + j % a.page;
       const T* kr = cache + slot * Dk;
       float acc = 0.f;
-      for (int c = 0; c < Dk; ++c) acc += q[c] * a_to_f(kr[c]);
+      if (a.ql_vec) {                              // rows of whole 16-byte chunks: 8 bf16 or 4 floats per load
+        constexpr int PER = 16 / static_cast<int>(sizeof(T));
+        const uint4* k4 = reinterpret_cast<const uint4*>(kr);
+        for (int c4 = 0; c4 < Dk / PER; ++c4) acc += dot_chunk<T>(k4[c4], q + c4 * PER);
+      } else {
+        for (int c = 0; c < Dk; ++c) acc += q[c] * a_to_f(kr[c]);
+      }
       s = acc;
     }
     const float mn = fmaxf(m, warp_max(s));
@@ -614,6 +632,9 @@ extern "C" int b2tts_latent_attn(const void* ql, int64_t ql_tok, int64_t ql_head
     }
     return B2TTS_OK;
   }
+  // (plain kernel) ql_vec: the cache rows can be read 16 bytes at a time
+  a.ql_vec = reinterpret_cast<uintptr_t>(cache) % 16 == 0 &&
+             ((kv_rank + rot_dim) * (dtype == B2TTS_DTYPE_BF16 ? 2 : 4)) % 16 == 0;
   const size_t smem = static_cast<size_t>(LA_WARPS) * (kv_rank + rot_dim) * sizeof(float);
   B2_REQUIRE(smem <= 48 * 1024, B2TTS_EUNSUPPORTED, "latent_attn: key size %d too large", kv_rank + rot_dim);
   const dim3 grid((static_cast<unsigned>(max_new) * heads + LA_WARPS - 1) / LA_WARPS, n_seqs);
