@@ -121,12 +121,12 @@ def ridevik_config(s: dict, moe: bool):
     mlp = {"kind": "dense", "ff": ff} if not moe else \
         {"kind": "moe", "expert": {"ff": ff // 3}, "router": {"experts": 16, "top": 2}}
     base = {"heads": s["heads"], "dim": d, "rot_dim": d // 2, "vdim": d, "kv_rank": 4 * d, "scale": (d + d // 2) ** -0.5}
-    causal = {"type": "latent_attention_2", "mlp": mlp, "mixer": dict(base, rot={"base": 1e6, "dims": d // 2})}
+    causal = {"type": "latent_attention_2", "mlp": mlp, "mixer": dict(base, rot={"base": 5e5, "dims": d // 2})}
     window = {"type": "latent_attention", "mlp": mlp,
               "mixer": dict(base, q_rank=s["width"] // 2, mask={"size": WINDOW},
-                            rot={"base": 1e4, "dims": d // 2, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}})}
+                            rot={"base": 1e4, "dims": d // 2, "scaling": {"factor": 8.0, "original": 2048, "fast": 16.0, "slow": 2.0}})}
     return RidevikConfig.from_dict({"architecture": "Ridevik", "vocab": 3072, "width": s["width"], "embedding": {"scale": 1.0},
-                                    "norm": {"eps": 1e-6, "groups": 2}, "layers": [causal, window] * (LAYERS // 2)})
+                                    "norm": {"eps": 1e-6, "groups": 4}, "layers": [causal, window] * (LAYERS // 2)})
 
 
 def bench_talker(s: dict, device: str) -> dict:

@@ -548,7 +548,7 @@ static cudaError_t launch_latent_mma(const LatentAttnArgs& a, const LatentMmaSme
   auto kern = latent_attn_mma_kernel<NW, NT, KSMAX>;
   const LatentMmaSmem sm = KSMAX == 0 ? latent_mma_smem(a.r, a.dr, 1) : sm_in;
   if (sm.total > 48 * 1024) {
-    static bool raised = false;                  // one attribute per kernel instance: raise it to the card's limit once
+    static bool raised = false;                  // one attribute per kernel instance: raise it to the device's limit once
     if (!raised) {
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
       if (e != cudaSuccess) return e;

@@ -208,7 +208,7 @@ def _attn_case(nat, H, r, dr, window, page, seqs, dtype=torch.float32, spike=Non
     return worst
 
 
-@pytest.mark.parametrize("H,r,dr", [(3, 24, 8), (8, 64, 32), (5, 40, 6), (16, 128, 16)])
+@pytest.mark.parametrize("H,r,dr", [(3, 24, 8), (8, 64, 24), (5, 40, 6), (16, 128, 16)])
 @pytest.mark.parametrize("window", [0, 1, 7, 64, 65])
 def test_latent_attention_prompts_portions_and_decoded_tokens_in_one_launch(nat, H, r, dr, window):
     seqs = [(0, 70), (50, 19), (129, 1), (64, 1), (0, 1), (63, 2)]
@@ -216,7 +216,7 @@ def test_latent_attention_prompts_portions_and_decoded_tokens_in_one_launch(nat,
     assert _attn_case(nat, H, r, dr, window, 64, seqs, seed=H + window + 1, rot_dims=dr - 2) < 2e-5
 
 
-@pytest.mark.parametrize("H,r,dr", [(8, 64, 32), (4, 96, 16), (16, 128, 16), (3, 32, 8), (20, 64, 8), (2, 256, 64), (1, 160, 24)])
+@pytest.mark.parametrize("H,r,dr", [(8, 64, 16), (4, 96, 8), (16, 128, 16), (3, 32, 8), (20, 64, 8), (2, 256, 64), (1, 160, 24)])
 @pytest.mark.parametrize("window", [0, 1, 7, 64, 65, 130])
 def test_tensor_core_latent_attention_against_plain_model_and_plain_kernel(nat, H, r, dr, window):
     """The bfloat16 tensor-core kernel (forced) on mixed steps: tiles of several tokens (fewer than 16 heads), of one
@@ -228,7 +228,7 @@ def test_tensor_core_latent_attention_against_plain_model_and_plain_kernel(nat, 
             assert e < 2e-2, (path, e)
 
 
-@pytest.mark.parametrize("H,r,dr", [(8, 64, 32), (4, 96, 16), (20, 64, 8)])
+@pytest.mark.parametrize("H,r,dr", [(8, 64, 16), (4, 96, 24), (20, 64, 8)])
 @pytest.mark.parametrize("window", [0, 70, 300])
 def test_decode_steps_whose_keys_are_cut_into_ranges_and_merged(nat, H, r, dr, window):
     """A decode step on the tensor-core kernel with each sequence's keys cut into 2, 3 or 8 ranges (more ranges than some
@@ -259,7 +259,7 @@ def test_one_key_that_takes_the_softmax_at_window_edges_and_page_borders(nat, dt
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
 def test_far_key_among_hundreds_and_a_sink_that_swallows_a_head(nat, dtype, tol):
-    H, r, dr = 8, 64, 32
+    H, r, dr = 8, 64, 16
     for window, back in [(0, 899), (700, 699), (700, 700)]:
         seqs = [(900, 1), (880, 21)]
         assert _attn_case(nat, H, r, dr, window, 64, seqs, dtype=dtype, spike=(0, 900 - back), seed=back) < tol
@@ -373,7 +373,7 @@ CONFIGS = {
                                               kinds=("moe", "dense"), n_layers=2, embedding_scale=1.0),
     "window_only_layers": dict(types=("latent_attention",), window=17, n_layers=2, kinds=(None, "dense")),
     "causal_only_layers": dict(types=("latent_attention_2",), n_layers=2, kinds=("dense", None)),
-    "tensor_core_shapes": dict(width=128, heads=(8, 4), dim=(32, 16), rot_dim=(16, 16), vdim=(32, 32), kv_rank=(64, 96), q_rank=32,
+    "tensor_core_shapes": dict(width=128, heads=(4, 2), dim=(32, 16), rot_dim=(16, 24), vdim=(32, 48), kv_rank=(128, 96), q_rank=32,
                                ff=128, expert_ff=64, window=20, kinds=("dense", "moe"), n_layers=2, vocab=128),
 }
 
