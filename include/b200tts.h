@@ -502,6 +502,8 @@ B2TTS_API int b2tts_latent_attn(const void* ql, int64_t ql_tok, int64_t ql_head,
  * a count that fills the GPU for a decode step (1 for anything else). */
 B2TTS_API int b2tts_latent_attn_splits(int n_seqs, int max_new, int heads);
 B2TTS_API size_t b2tts_latent_attn_workspace_floats(int n_seqs, int max_new, int heads, int kv_rank, int splits);
+/* How many bounded waits for a key tile ran out inside the tensor-core kernel since load (0 in a healthy run); synchronises. */
+B2TTS_API int b2tts_latent_attn_timeouts(void);
 /* out[t, h * vdim + d] = v[t * v_tok + h * v_head + d] * sigmoid(gate[t * ldg + h * vdim + d]) (gate null: the copy alone). */
 B2TTS_API int b2tts_gate_heads(const void* v, int64_t v_tok, int64_t v_head, const void* gate, int64_t ldg, void* out, int n,
                                int heads, int vdim, int dtype, void* stream);

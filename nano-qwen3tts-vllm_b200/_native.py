@@ -91,6 +91,7 @@ def _load():
         "b2tts_latent_prep": (I, [P, L, I, I, P, P, P, P, F, P, P, P, I, I, I, I, I, F, I, P]),
         "b2tts_latent_attn": (I, [P, L, L, P, L, L, P, P, L, L, P, P, F, I, P, P, P, P, L, I, I, I, I, I, I, I, F, I, I, I, P, P]),
         "b2tts_latent_attn_splits": (I, [I, I, I]),
+        "b2tts_latent_attn_timeouts": (I, []),
         "b2tts_latent_attn_workspace_floats": (Z, [I, I, I, I, I]),
         "b2tts_gate_heads": (I, [P, L, L, P, L, P, I, I, I, I, P]),
         "b2tts_group_norm_residual": (I, [P, P, P, P, I, P, I, F, P, I, I, I, P]),
@@ -835,6 +836,11 @@ def latent_attn(ql, ql_strides, qr, qr_strides, cache, out, out_strides, sink, f
                                   rot_mult, rot_dims, lay.seq_start.data_ptr(), lay.seq_pos0.data_ptr(), lay.seq_len.data_ptr(),
                                   lay.block_tables.data_ptr(), lay.block_tables.stride(0), lay.n_seqs, lay.max_new, heads,
                                   kv_rank, rot_dim, page, window, scale, dt, path, splits, _ptr(ws), _stream()), "latent_attn")
+
+
+def latent_attn_timeouts() -> int:
+    """Bounded waits of the tensor-core latent attention that ran out since the library was loaded (0 when healthy)."""
+    return _load().b2tts_latent_attn_timeouts()
 
 
 def gate_heads(v, v_strides, gate, out, heads, vdim):

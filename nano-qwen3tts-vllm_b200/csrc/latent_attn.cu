@@ -170,9 +170,20 @@ __device__ __forceinline__ void ldsm_x2_a(uint32_t& r0, uint32_t& r1, uint32_t a
 __device__ __forceinline__ void ldsm_x2_t_a(uint32_t& r0, uint32_t& r1, uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
 }
-__device__ __forceinline__ void cp_async_16_a(uint32_t dst, const void* gsrc, bool ok) {
-  const int bytes = ok ? 16 : 0;
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst), "l"(gsrc), "r"(bytes) : "memory");
+
+// How often a wait for a key tile ran out (it never should: the copies are this CTA's own); read by b2tts_latent_attn_timeouts().
+__device__ int g_latent_attn_timeouts = 0;
+
+// Wait for phase `parity` of an mbarrier, giving up after a bounded number of polls.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (int i = 0; i < (1 << 20); ++i) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+    if (ok) return true;
+  }
+  return false;
 }
 
 struct LatentMmaSmem {
@@ -187,7 +198,7 @@ static LatentMmaSmem latent_mma_smem(int r, int dr, int stages = 2) {
   m.s_off = m.k_off + stages * LM_KT * m.ldk * 2;
   m.p_off = m.s_off + 16 * LM_KT * 4;
   m.st_off = m.p_off + 16 * (LM_KT + 8) * 2;
-  m.total = m.st_off + 16 * 4 * 4;
+  m.total = m.st_off + 16 * 4 * 4 + 2 * 8;      // row statistics, then one mbarrier per key stage
   return m;
 }
 
@@ -225,31 +236,33 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
   const int tps = (n_tiles + a.splits - 1) / a.splits;
   const int t_begin = blockIdx.z * tps, t_end = min(n_tiles, t_begin + tps);
 
-  // a warp copies whole rows: the page lookup is once per key and uniform over the warp, the lanes stride over the
-  // row's 16-byte chunks; keys past the last query and the padding chunk are zero-filled
-  // lane i looks up the i-th key of this warp's share of a tile; the lookup runs one tile ahead of the copies, so that
-  // its latency is never waited for
+  // Key tiles arrive by bulk copies (the TMA unit: no load instructions, no registers, whole rows of r + dr numbers),
+  // one per key, issued by the first 64 / NW lanes of every warp and counted on the stage's mbarrier.  Lane i owns the
+  // i-th key of its warp's share; its table lookup runs one tile ahead of the copy.  Keys past the last query repeat
+  // the last key (finite numbers; their weights are zero), so a tile is always 64 whole rows.
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + sm.st_off + 16 * 4 * 4);
+  constexpr int STAGES = KSMAX > 0 ? 2 : 1;
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < STAGES; ++i) mbar_init(&bars[i], 1);
+    mbar_fence_init();
+  }
+  if (dkp > Dk)                                   // the padding chunk after every row is never copied to: zero it once
+    for (int i = tid; i < STAGES * LM_KT; i += NW * 32) *reinterpret_cast<uint4*>(ks + i * ldk + Dk) = make_uint4(0u, 0u, 0u, 0u);
+  __syncthreads();
   auto lookup = [&](int t) -> long long {
     long long off = -1;
     if (lane < LM_KT / NW && t < t_end) {
-      const int j = j_lo + t * LM_KT + warp + lane * NW;
-      if (j <= pos_last) off = (static_cast<long long>(bt[j / a.page]) * a.page + j % a.page) * Dk;
+      const int j = min(j_lo + t * LM_KT + warp + lane * NW, pos_last);
+      off = (static_cast<long long>(bt[j / a.page]) * a.page + j % a.page) * Dk;
     }
     return off;
   };
   const uint32_t ks_u = smem_u32(ks), ps_u = smem_u32(ps);
+  const uint32_t row_bytes = static_cast<uint32_t>(Dk) * 2u;
   auto load_tile = [&](long long my, int stage) {
-    const uint32_t dst = ks_u + static_cast<uint32_t>(stage * LM_KT * ldk + warp * ldk + lane * 8) * 2u;
-    const int cpr = dkp / 8, real = Dk / 8;
-#pragma unroll
-    for (int i = 0; i < LM_KT / NW; ++i) {
-      const long long off = __shfl_sync(0xffffffffu, my, i);
-      const bool in = off >= 0;
-      const __nv_bfloat16* src = cache + (in ? off : 0) + lane * 8;
-      uint32_t d = dst + static_cast<uint32_t>(i * NW * ldk) * 2u;
-      for (int ch = lane; ch < cpr; ch += 32, d += 512u, src += 256) cp_async_16_a(d, src, in && ch < real);
-    }
-    cp_async_commit();
+    if (tid == 0) mbar_expect_tx(&bars[stage], LM_KT * row_bytes);
+    if (my >= 0) bulk_g2s(ks + (stage * LM_KT + warp + lane * NW) * ldk, cache + my, row_bytes, &bars[stage]);
   };
   long long slots_next = lookup(t_begin);
   if (t_begin < t_end) {
@@ -352,17 +365,19 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
     if (QREG && t + 1 < t_end) {
       load_tile(slots_next, stage ^ 1);
       slots_next = lookup(t + 2);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
     }
-    __syncthreads();
+    const int use = QREG ? (t - t_begin) >> 1 : t - t_begin;      // how often this stage has been filled before
+    const bool arrived = mbar_wait_bounded(&bars[stage], use & 1);
+    if (__syncthreads_or(!arrived)) {              // never expected; all threads leave together
+      if (tid == 0) atomicAdd(&g_latent_attn_timeouts, 1);
+      break;
+    }
     // ---- S = Q K^T for this warp's keys
-    float sc[SN][2][4];                          // two accumulators per n-tile: alternate k-steps do not wait on each other
+    float sc[SN][4][4];                          // four accumulators per n-tile: the k-steps of a group do not wait on each other
 #pragma unroll
     for (int i = 0; i < SN; ++i)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) sc[i][0][e] = sc[i][1][e] = 0.f;
+      for (int e = 0; e < 4; ++e) sc[i][0][e] = sc[i][1][e] = sc[i][2][e] = sc[i][3][e] = 0.f;
     const uint32_t kt_u = ks_u + static_cast<uint32_t>(stage * LM_KT * ldk) * 2u;
     const uint32_t k_lane = kt_u + static_cast<uint32_t>((warp * SN * 8 + (lane & 7)) * ldk + ((lane >> 3) & 1) * 8) * 2u;
     if (QREG) {
@@ -381,7 +396,7 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
           for (int u = 0; u < 4; ++u) {
             if ((u0 + u) * 16 < dkp) {
 #pragma unroll
-              for (int i = 0; i < SN; ++i) mma_bf16_16816(sc[i][u & 1], qf[QREG ? u0 + u : 0], bf[u][i][0], bf[u][i][1]);
+              for (int i = 0; i < SN; ++i) mma_bf16_16816(sc[i][u], qf[QREG ? u0 + u : 0], bf[u][i][0], bf[u][i][1]);
             }
           }
         }
@@ -401,7 +416,7 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
         for (int u = 0; u < 4; ++u) {
           if (k0 + 16 * u < dkp) {
 #pragma unroll
-            for (int i = 0; i < SN; ++i) mma_bf16_16816(sc[i][u & 1], af[u], bf[u][i][0], bf[u][i][1]);
+            for (int i = 0; i < SN; ++i) mma_bf16_16816(sc[i][u], af[u], bf[u][i][0], bf[u][i][1]);
           }
         }
       }
@@ -409,10 +424,10 @@ latent_attn_mma_kernel(const LatentAttnArgs a, const LatentMmaSmem sm) {
 #pragma unroll
     for (int i = 0; i < SN; ++i) {
       const int n0 = (warp * SN + i) * 8 + (lane & 3) * 2, r0 = lane >> 2;
-      ss[r0 * LM_KT + n0] = sc[i][0][0] + sc[i][1][0];
-      ss[r0 * LM_KT + n0 + 1] = sc[i][0][1] + sc[i][1][1];
-      ss[(r0 + 8) * LM_KT + n0] = sc[i][0][2] + sc[i][1][2];
-      ss[(r0 + 8) * LM_KT + n0 + 1] = sc[i][0][3] + sc[i][1][3];
+      ss[r0 * LM_KT + n0] = (sc[i][0][0] + sc[i][1][0]) + (sc[i][2][0] + sc[i][3][0]);
+      ss[r0 * LM_KT + n0 + 1] = (sc[i][0][1] + sc[i][1][1]) + (sc[i][2][1] + sc[i][3][1]);
+      ss[(r0 + 8) * LM_KT + n0] = (sc[i][0][2] + sc[i][1][2]) + (sc[i][2][2] + sc[i][3][2]);
+      ss[(r0 + 8) * LM_KT + n0 + 1] = (sc[i][0][3] + sc[i][1][3]) + (sc[i][2][3] + sc[i][3][3]);
     }
     __syncthreads();
     // ---- running maximum, sum and weights, in float; a warp takes rows warp, warp + NW, ..
@@ -655,4 +670,12 @@ extern "C" int b2tts_latent_attn_splits(int n_seqs, int max_new, int heads) {
 extern "C" size_t b2tts_latent_attn_workspace_floats(int n_seqs, int max_new, int heads, int kv_rank, int splits) {
   const int hpc = heads < 16 ? heads : 16, G = 16 / hpc;
   return static_cast<size_t>(n_seqs) * ((max_new + G - 1) / G) * ((heads + 15) / 16) * splits * 16 * (kv_rank + 2);
+}
+
+/* Number of key-tile waits of the tensor-core kernel that ran out since the library was loaded (0 in a healthy run).
+ * Synchronises the device. */
+extern "C" int b2tts_latent_attn_timeouts(void) {
+  int v = -1;
+  if (cudaMemcpyFromSymbol(&v, b2::lat::g_latent_attn_timeouts, sizeof(int)) != cudaSuccess) return -1;
+  return v;
 }
