@@ -53,6 +53,17 @@ embed_scale_kernel(const int32_t* __restrict__ tokens, const T* __restrict__ emb
   for (int c = threadIdx.x; c < cols; c += blockDim.x) x[row * cols + c] = to_f(er[c]) * scale;
 }
 
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 v;
+  v.x = *reinterpret_cast<const uint32_t*>(&lo);
+  v.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = v;
+}
+
 // ------------------------------------------------------------------ token shift
 // out[t] = x[t] + (prev - x[t]) * mu, prev = the same layer's input row of the previous position: x[t - 1] when that
 // position runs in this step, the sequence's state slot when it ran in an earlier step, zero at position 0 (by position:
@@ -79,6 +90,21 @@ token_shift_kernel(const float* __restrict__ x, const float* __restrict__ mu, fl
   const float* xr = x + t * cols;
   const float* pr = first ? srow : xr - cols;
   const float* last = x + static_cast<size_t>(start + len - 1) * cols;
+  if (cols % 4 == 0) {                                                    // rows of whole float4: 16-byte loads, 8- or 16-byte stores
+    const float4* x4 = reinterpret_cast<const float4*>(xr);
+    const float4* p4 = reinterpret_cast<const float4*>(pr);
+    const float4* m4 = reinterpret_cast<const float4*>(mu);
+    const float4* l4 = reinterpret_cast<const float4*>(last);
+    float4* s4 = reinterpret_cast<float4*>(srow);
+    for (int c = threadIdx.x; c < cols / 4; c += blockDim.x) {
+      const float4 cur = x4[c], m = m4[c];
+      const float4 prev = pos > 0 ? p4[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+      store4(orow + 4 * c, cur.x + (prev.x - cur.x) * m.x, cur.y + (prev.y - cur.y) * m.y, cur.z + (prev.z - cur.z) * m.z,
+             cur.w + (prev.w - cur.w) * m.w);
+      if (first) s4[c] = l4[c];                                           // same thread read s4[c] just above
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < cols; c += blockDim.x) {
     const float cur = xr[c];
     const float prev = pos > 0 ? pr[c] : 0.f;

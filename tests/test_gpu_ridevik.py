@@ -95,11 +95,12 @@ def test_embedding_group_norm_residual_and_activations(nat, dtype, cols, groups)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_token_shift_in_portions_through_a_reused_slot(nat, dtype):
+@pytest.mark.parametrize("D", [70, 72, 1028])
+def test_token_shift_in_portions_through_a_reused_slot(nat, dtype, D):
     """Two sequences cut into portions of 1, 2, 3, 7 ... tokens; their previous rows travel through state slots that
     hold another owner's rows at the start (position 0 must read zero all the same)."""
     g = torch.Generator().manual_seed(5)
-    D, T = 70, 33
+    T = 33
     xs = [torch.randn(T, D, generator=g), torch.randn(T, D, generator=g)]
     mu = torch.rand(D, generator=g)
     state = torch.full((3, D), 9.0, device=DEV)
